@@ -138,3 +138,123 @@ class Qwen2Config(ModelConfig):
             max_position_embeddings=int(raw.get("max_position_embeddings", 32768)),
             head_dim=int(raw.get("head_dim") or hidden // heads),
         )
+
+
+@dataclass(frozen=True)
+class ModovikLayer:
+    """One layer of a Modovik model: ``kind`` "attention" (softmax attention with a sink over the paged cache) or
+    "lightning" (linear attention with a decay per head over a state), the mixer's sizes, and the size of the
+    dense feed-forward (0: the layer has none)."""
+
+    kind: str
+    heads: int
+    dim: int                       # query/key entries per head
+    vdim: int                      # value entries per head
+    kv_heads: int = 0              # attention: key/value heads
+    scale: float = 0.0             # attention: factor on q . k
+    rot_dims: int = 0              # attention: leading dims of a head that are rotated
+    rot_base: float = 10000.0
+    kv_from: int = -1              # attention: the layer whose cached keys and values this one reads (-1: its own)
+    decay: tuple = ()              # lightning: one constant per head
+    ff: int = 0
+
+
+@dataclass(frozen=True)
+class ModovikConfig(ModelConfig):
+    """A Modovik decoder: an embedding, layers in the order of ``layers`` whose norms sit on the branch outputs,
+    a final norm and a head.  ``config.json`` keys: ``vocab``, ``width``, ``norm.eps`` and ``layers``, a list of
+    ``{"type", "mixer": {...}, "mlp": {"kind": "dense", "ff": n} | null}`` with the mixer's keys ``heads``, ``dim``,
+    ``vdim`` and, for attention, ``kv_heads``, ``scale``, ``rot: {"dims", "base"}``, optionally ``kv_from``; for
+    lightning, ``decay``."""
+
+    architecture: ClassVar[str] = "Modovik"
+
+    vocab: int
+    width: int
+    norm_eps: float
+    layers: tuple
+
+    def __post_init__(self):
+        _positive("vocab", self.vocab)
+        _positive("width", self.width)
+        if not self.norm_eps > 0:
+            raise ConfigError(f"config.json: norm.eps must be positive, got {self.norm_eps}")
+        if not self.layers:
+            raise ConfigError("config.json: layers is empty")
+        for i, L in enumerate(self.layers):
+            where = f"config.json: layers[{i}]"
+            if L.kind not in ("attention", "lightning"):
+                raise ConfigError(f"{where}.type {L.kind!r}: known are 'attention' and 'lightning'")
+            for name in ("heads", "dim", "vdim"):
+                if getattr(L, name) <= 0:
+                    raise ConfigError(f"{where}.mixer.{name} must be positive")
+            if L.ff < 0:
+                raise ConfigError(f"{where}.mlp.ff must be positive")
+            if L.kind == "lightning":
+                if len(L.decay) != L.heads:
+                    raise ConfigError(f"{where}.mixer.decay has {len(L.decay)} entries for {L.heads} heads")
+                continue
+            if L.kv_heads <= 0 or L.heads % L.kv_heads:
+                raise ConfigError(f"{where}.mixer: heads ({L.heads}) must be a multiple of kv_heads ({L.kv_heads})")
+            if L.rot_dims < 0 or L.rot_dims % 2 or L.rot_dims > L.dim:
+                raise ConfigError(f"{where}.mixer.rot.dims ({L.rot_dims}) must be even and at most dim ({L.dim})")
+            if L.rot_dims and not L.rot_base > 0:
+                raise ConfigError(f"{where}.mixer.rot.base must be positive")
+            if L.kv_from >= 0:
+                src = self.layers[L.kv_from] if L.kv_from < len(self.layers) else None
+                if src is None or L.kv_from >= i or src.kind != "attention" or src.kv_from >= 0:
+                    raise ConfigError(f"{where}.mixer.kv_from ({L.kv_from}) must name an earlier attention layer with "
+                                      f"keys and values of its own")
+                if (src.kv_heads, src.dim, src.vdim, src.rot_dims, src.rot_base) != (L.kv_heads, L.dim, L.vdim, L.rot_dims, L.rot_base):
+                    raise ConfigError(f"{where}.mixer: head sizes and rotation must equal those of layer {L.kv_from}, "
+                                      f"whose keys and values it reads")
+
+    @classmethod
+    def from_dict(cls, raw: dict[str, Any]) -> "ModovikConfig":
+        norm = raw.get("norm")
+        if not isinstance(norm, dict):
+            raise ConfigError("config.json: required key 'norm' (with 'eps') is missing")
+        layers_raw = raw.get("layers")
+        if not isinstance(layers_raw, (list, tuple)):
+            raise ConfigError("config.json: required key 'layers' is missing")
+        layers = []
+        for i, entry in enumerate(layers_raw):
+            where = f"layers[{i}]"
+            if not isinstance(entry, dict) or not isinstance(entry.get("mixer"), dict):
+                raise ConfigError(f"config.json: {where} needs 'type' and 'mixer'")
+            m = entry["mixer"]
+            kind = str(entry.get("type"))
+            mlp = entry.get("mlp")
+            ff = 0
+            if mlp is not None:
+                if not isinstance(mlp, dict) or mlp.get("kind", "dense") != "dense":
+                    raise ConfigError(f"config.json: {where}.mlp.kind {mlp.get('kind') if isinstance(mlp, dict) else mlp!r}: only 'dense' is known")
+                ff = _positive(f"{where}.mlp.ff", _require(mlp, "ff"))
+            fields = dict(kind=kind, heads=_require(m, "heads"), dim=_require(m, "dim"), vdim=_require(m, "vdim"), ff=ff)
+            if kind == "lightning":
+                decay = m.get("decay")
+                if not isinstance(decay, (list, tuple)):
+                    raise ConfigError(f"config.json: {where}.mixer.decay is missing")
+                fields["decay"] = tuple(float(d) for d in decay)
+            elif kind == "attention":
+                rot = m.get("rot") or {}
+                fields.update(kv_heads=int(m.get("kv_heads") or fields["heads"]), scale=_require(m, "scale", float),
+                              rot_dims=int(rot.get("dims", 0)), rot_base=float(rot.get("base", 10000.0)),
+                              kv_from=int(m["kv_from"]) if m.get("kv_from") is not None else -1)
+            layers.append(ModovikLayer(**fields))
+        return cls(vocab=_require(raw, "vocab"), width=_require(raw, "width"), norm_eps=_require(norm, "eps", float),
+                   layers=tuple(layers))
+
+    def to_dict(self) -> dict[str, Any]:
+        layers = []
+        for L in self.layers:
+            if L.kind == "lightning":
+                mixer = {"heads": L.heads, "dim": L.dim, "vdim": L.vdim, "decay": list(L.decay)}
+            else:
+                mixer = {"heads": L.heads, "kv_heads": L.kv_heads, "dim": L.dim, "vdim": L.vdim, "scale": L.scale,
+                         "rot": {"dims": L.rot_dims, "base": L.rot_base}}
+                if L.kv_from >= 0:
+                    mixer["kv_from"] = L.kv_from
+            layers.append({"type": L.kind, "mixer": mixer, "mlp": {"kind": "dense", "ff": L.ff} if L.ff else None})
+        return {"architecture": self.architecture, "vocab": self.vocab, "width": self.width,
+                "norm": {"eps": self.norm_eps}, "layers": layers}

@@ -1,6 +1,6 @@
 """One registry from an architecture's name to its configuration class and model builder.
 
-``config.json`` names its model class in ``architectures[0]``; everything in the
+``config.json`` names its model class in ``architectures[0]`` (or in a plain string ``architecture``); everything in the
 package that opens a model folder (engine, command line, trace replay, tests) goes
 through ``load_config`` and ``architecture`` here, so a new architecture is added by
 one ``register_architecture`` call and no other change.  The reference has a substring
@@ -56,6 +56,8 @@ def architecture_of(config: ModelConfig) -> Architecture:
 
 def config_from_dict(raw: dict[str, Any]) -> ModelConfig:
     archs = raw.get("architectures")
+    if isinstance(raw.get("architecture"), str) and not archs:
+        archs = [raw["architecture"]]      # some configurations name one class in a plain string
     if not archs or not isinstance(archs, (list, tuple)):
         raise ConfigError("config.json: key 'architectures' is missing or empty; it names the model class")
     return architecture(archs[0]).config_cls.from_dict(raw)
@@ -76,4 +78,4 @@ def _ensure_builtin() -> None:
     global _builtin_done
     if not _builtin_done:
         _builtin_done = True
-        from ..models import qwen2  # noqa: F401
+        from ..models import modovik, qwen2  # noqa: F401

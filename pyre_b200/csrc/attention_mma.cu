@@ -124,6 +124,8 @@ struct AttnParams {
     int uniform_len;             // > 0: every entry has exactly this many tokens (a decode step): no scan for the group
     int max_len;                 // > 0: only entries with at most this many tokens (longer ones go to the prefill kernel)
     float scale;
+    float sink_l2;               // score of a sink without a value, in units of log2(e): 2^(sink_l2 - max) joins every row's
+                                 // denominator once, where the row is normalised; -inf: no sink (the term is 0)
 };
 
 // CLUSTER: the n_splits CTAs of a (group, kv head) form one thread-block cluster and merge their
@@ -529,7 +531,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
         }
         const size_t th = (size_t)th_row;
         if (p.n_splits == 1) {
-            const float inv = 1.0f / L;
+            const float inv = 1.0f / (L + ex2(p.sink_l2 - m_use));
             *reinterpret_cast<uint2*>(p.out + th * HD + d) = make_uint2(pack_bf16(O[0] * inv, O[1] * inv), pack_bf16(O[2] * inv, O[3] * inv));
         } else if constexpr (CLUSTER) {
             // push this CTA's partial to the CTA that owns the output dims: slot [this rank][row][d - owner * cp]
@@ -578,7 +580,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
                     L += ml.y * f;
                     O += rx_o[(c * 16 + row) * cp + dl] * f;
                 }
-                p.out[(size_t)th_row * HD + d0 + dl] = __float2bfloat16_rn(O / L);
+                p.out[(size_t)th_row * HD + d0 + dl] = __float2bfloat16_rn(O / (L + ex2(p.sink_l2 - m_use)));
             }
         }
     }
@@ -593,7 +595,7 @@ constexpr int COMBINE_WARPS = 8;
 __global__ void __launch_bounds__(COMBINE_WARPS * 32)
 combine_splits_kernel(const float* part_acc, const float* part_ml,
                       __nv_bfloat16* out, int n_splits, int hd, int nh,
-                      const int* cu_seqlens, int n_seqs, int max_len) {
+                      const int* cu_seqlens, int n_seqs, int max_len, float sink_l2) {
     pdl_trigger();
     pdl_wait();
     const size_t th = blockIdx.x;
@@ -653,7 +655,7 @@ combine_splits_kernel(const float* part_acc, const float* part_ml,
             Ls += sm_l[w] * f;
             Os.x += o.x * f; Os.y += o.y * f; Os.z += o.z * f; Os.w += o.w * f;
         }
-        const float inv = 1.0f / Ls;
+        const float inv = 1.0f / (Ls + exp2f(sink_l2 - m_use));
         *reinterpret_cast<uint2*>(out + th * hd + 4 * lane) = make_uint2(pack_bf16(Os.x * inv, Os.y * inv), pack_bf16(Os.z * inv, Os.w * inv));
     }
 }
@@ -751,7 +753,7 @@ PYRE_API long long pyre_attention_mma_scratch_floats(int n_tokens, int nh, int h
 PYRE_API int pyre_paged_attention_mma(const void* q, const void* cache, void* out, float* scratch,
                                       const int* block_table, int bt_stride, const int* cu_seqlens,
                                       const int* positions, int n_tokens, int n_seqs, int nh, int nkv, int hd,
-                                      int page_size, int window, float scale, int n_splits, int max_len,
+                                      int page_size, int window, float scale, float sink, int n_splits, int max_len,
                                       long long n_pages, int uniform_len, int* err_flag, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hd % 16 || hd < 16 || hd > 128 || nkv <= 0 || nh % nkv || page_size <= 0 || n_splits < 1) return PYRE_ERR_UNSUPPORTED;
@@ -769,6 +771,7 @@ PYRE_API int pyre_paged_attention_mma(const void* q, const void* cache, void* ou
     p.positions = positions;
     p.bt_stride = bt_stride; p.n_seqs = n_seqs; p.nh = nh; p.nkv = nkv; p.page_size = page_size;
     p.window = window; p.n_splits = n_splits; p.scale = scale; p.max_len = max_len;
+    p.sink_l2 = sink * 1.44269504088896341f;
     p.page_shift = -1;
     if ((page_size & (page_size - 1)) == 0) { p.page_shift = 0; while ((1 << p.page_shift) < page_size) ++p.page_shift; }
     // TMA tiles: power-of-two pages, head size a multiple of 64 (the 128-byte swizzle span), aligned base
@@ -805,7 +808,7 @@ PYRE_API int pyre_paged_attention_mma(const void* q, const void* cache, void* ou
     }
     if (rc) return rc;
     if (n_splits > 1 && !use_cluster) {
-        pyre_launch(combine_splits_kernel, dim3(n_tokens * nh), dim3(COMBINE_WARPS * 32), 0, stream, p.part_acc, p.part_ml, p.out, n_splits, hd, nh, cu_seqlens, n_seqs, max_len);
+        pyre_launch(combine_splits_kernel, dim3(n_tokens * nh), dim3(COMBINE_WARPS * 32), 0, stream, p.part_acc, p.part_ml, p.out, n_splits, hd, nh, cu_seqlens, n_seqs, max_len, p.sink_l2);
         PYRE_LAUNCH_CHECK();
     }
     return 0;

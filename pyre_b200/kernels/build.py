@@ -35,6 +35,8 @@ LIBRARIES = {
     "attention_prefill": "attention_prefill.cu",
     "attention_tc": "attention_tc.cu",
     "attention_mma_noalloc": "attention_mma_noalloc.cu",
+    "blockops": "blockops.cu",
+    "linear_attention": "linear_attention.cu",
 }
 
 HEADERS = ["common.cuh", "attention_mma_noalloc.h"]

@@ -38,11 +38,18 @@ SIGNATURES: dict[str, tuple[str, list]] = {
     "pyre_scale_rows": ("elementwise", [P, P, I, P, I, I, F, P]),
     "pyre_sample": ("sampling", [P, LL, P, P, P, P, I, I, P, P]),
     "pyre_sample_slices": ("sampling", [I]),
-    "pyre_paged_attention_generic": ("attention_generic", [P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, LL, P, P]),
+    "pyre_paged_attention_generic": ("attention_generic", [P, P, P, P, I, P, P, I, I, I, I, I, I, F, F, I, LL, P, P]),
     "pyre_sgemm_nt": ("gemm_f32", [P, LL, P, LL, P, LL, P, I, I, I, P]),
-    "pyre_paged_attention_mma": ("attention_mma", [P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, I, LL, I, P, P]),
-    "pyre_attention_prefill_tc": ("attention_tc", [P, P, P, P, I, P, P, I, I, I, I, I, I, I, LL, I, F, I, I, P, P, P, P]),
-    "pyre_attention_prefill": ("attention_prefill", [P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, LL, P, P]),
+    "pyre_paged_attention_mma": ("attention_mma", [P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, F, I, I, LL, I, P, P]),
+    "pyre_attention_prefill_tc": ("attention_tc", [P, P, P, P, I, P, P, I, I, I, I, I, I, I, LL, I, F, F, I, I, P, P, P, P]),
+    "pyre_attention_prefill": ("attention_prefill", [P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, F, I, LL, P, P]),
+    "pyre_cast_rows": ("blockops", [P, P, LL, I, P]),
+    "pyre_norm_add": ("blockops", [P, P, P, I, LL, P, P, I, I, F, I, P]),
+    "pyre_activation": ("blockops", [P, P, LL, I, I, P]),
+    "pyre_qk_norm_rope_write": ("blockops", [P, LL, I, I, I, P, P, F, P, P, P, P, P, I, I, I, I, I, I, I, I, I, LL, P, P]),
+    "pyre_sigmoid_gate": ("blockops", [P, I, P, LL, I, P, I, I, I, I, P]),
+    "pyre_rmsnorm_gate": ("blockops", [P, P, P, LL, I, P, I, I, F, I, P]),
+    "pyre_linear_attention_scan": ("linear_attention", [P, LL, I, I, I, P, P, P, P, P, I, I, I, I, I, I, I, P]),
 }
 
 _ERRORS = {100001: "bad argument", 100002: "unsupported size"}
@@ -62,6 +69,8 @@ DEFAULT_CLASS = {
     "pyre_feed_tokens": "feed", "pyre_delay": "delay", "pyre_gemm_tc": "product", "pyre_sgemm_nt": "product", "pyre_scale_rows": "norm", "pyre_sample": "sampler",
     "pyre_paged_attention_generic": "attention", "pyre_paged_attention_mma": "attention",
     "pyre_attention_prefill_tc": "attention", "pyre_attention_prefill": "attention",
+    "pyre_cast_rows": "norm", "pyre_norm_add": "norm", "pyre_activation": "activation", "pyre_qk_norm_rope_write": "rotary+write",
+    "pyre_sigmoid_gate": "gate", "pyre_rmsnorm_gate": "gate", "pyre_linear_attention_scan": "linear_attention",
 }
 
 

@@ -366,8 +366,9 @@ def sample(logits: torch.Tensor, temperature: "torch.Tensor | None" = None, seed
 def paged_attention_generic(q: torch.Tensor, cache_layer: torch.Tensor, block_table: torch.Tensor,
                             seq_of_token: torch.Tensor, positions: torch.Tensor, n_heads: int, n_kv_heads: int,
                             head_dim: int, scale: float, window: "int | None" = None,
-                            out: "torch.Tensor | None" = None) -> torch.Tensor:
-    """Exact fp32-arithmetic attention of every query token over its sequence's pages."""
+                            out: "torch.Tensor | None" = None, sink: "float | None" = None) -> torch.Tensor:
+    """Exact fp32-arithmetic attention of every query token over its sequence's pages.  ``sink``: the score of a
+    sink that has no value: exp(sink) joins every softmax denominator (None: no sink)."""
     _check(q, "q", dim=2)
     _check(cache_layer, "cache_layer", q.dtype, 5)
     _check(block_table, "block_table", torch.int32, 2)
@@ -387,9 +388,14 @@ def paged_attention_generic(q: torch.Tensor, cache_layer: torch.Tensor, block_ta
         out = torch.empty_like(q)
     lib.call("pyre_paged_attention_generic", q.data_ptr(), cache_layer.data_ptr(), out.data_ptr(),
              block_table.data_ptr(), block_table.stride(0), seq_of_token.data_ptr(), positions.data_ptr(), T,
-             n_heads, n_kv_heads, head_dim, page_size, int(window or 0), float(scale), _dt(q.dtype), cache_layer.shape[0],
+             n_heads, n_kv_heads, head_dim, page_size, int(window or 0), float(scale), _sink(sink), _dt(q.dtype), cache_layer.shape[0],
              device_error_flag(q.device).data_ptr(), _stream())
     return out
+
+
+def _sink(sink: "float | None") -> float:
+    """The kernels' encoding of 'no sink': a score of minus infinity, whose term in the denominator is zero."""
+    return float("-inf") if sink is None else float(sink)
 
 
 MMA_MAX_HEAD_DIM = 128
@@ -458,7 +464,8 @@ def paged_attention_mma(q: torch.Tensor, cache_layer: torch.Tensor, block_table:
                         cu_seqlens: torch.Tensor, positions: torch.Tensor, n_seqs: int, n_heads: int,
                         n_kv_heads: int, head_dim: int, scale: float, window: "int | None" = None,
                         n_splits: int = 1, out: "torch.Tensor | None" = None,
-                        scratch: "torch.Tensor | None" = None, max_len: int = 0, uniform_len: int = 0) -> torch.Tensor:
+                        scratch: "torch.Tensor | None" = None, max_len: int = 0, uniform_len: int = 0,
+                        sink: "float | None" = None) -> torch.Tensor:
     """bfloat16 attention on the tensor cores over the block table (decode tokens and
     prompt portions alike); ``n_splits`` > 1 splits each sequence's keys over CTAs and needs
     ``T * nh * n_splits * (hd + 2)`` floats of scratch (allocated here if not given)."""
@@ -490,7 +497,7 @@ def paged_attention_mma(q: torch.Tensor, cache_layer: torch.Tensor, block_table:
             raise ValueError(f"scratch must be {need} contiguous floats")
     lib.call("pyre_paged_attention_mma", q.data_ptr(), cache_layer.data_ptr(), out.data_ptr(), _ptr(scratch),
              block_table.data_ptr(), block_table.stride(0), cu_seqlens.data_ptr(), positions.data_ptr(), T, n_seqs,
-             n_heads, n_kv_heads, head_dim, page_size, int(window or 0), float(scale), n_splits, int(max_len),
+             n_heads, n_kv_heads, head_dim, page_size, int(window or 0), float(scale), _sink(sink), n_splits, int(max_len),
              cache_layer.shape[0], int(uniform_len), device_error_flag(q.device).data_ptr(), _stream())
     return out
 
@@ -502,7 +509,7 @@ PREFILL_MIN_LEN = 32     # entries with at least this many tokens go to the prom
 def attention_prefill(q: torch.Tensor, cache_layer: torch.Tensor, block_table: torch.Tensor, cu_seqlens: torch.Tensor,
                       positions: torch.Tensor, n_seqs: int, n_long_tokens: int, n_heads: int, n_kv_heads: int,
                       head_dim: int, scale: float, window: "int | None", out: torch.Tensor,
-                      min_len: int = PREFILL_MIN_LEN) -> torch.Tensor:
+                      min_len: int = PREFILL_MIN_LEN, sink: "float | None" = None) -> torch.Tensor:
     """bfloat16 attention of the entries with at least ``min_len`` tokens (64 queries of a head
     per CTA, keys and values tiled through shared memory); writes only those entries' rows of ``out``."""
     _check(q, "q", torch.bfloat16, 2)
@@ -522,7 +529,7 @@ def attention_prefill(q: torch.Tensor, cache_layer: torch.Tensor, block_table: t
         raise ValueError("out, cu_seqlens and positions do not match the batch")
     lib.call("pyre_attention_prefill", q.data_ptr(), cache_layer.data_ptr(), out.data_ptr(), block_table.data_ptr(),
              block_table.stride(0), cu_seqlens.data_ptr(), positions.data_ptr(), int(n_long_tokens), n_seqs, n_heads,
-             n_kv_heads, head_dim, page_size, int(window or 0), float(scale), int(min_len), cache_layer.shape[0],
+             n_kv_heads, head_dim, page_size, int(window or 0), float(scale), _sink(sink), int(min_len), cache_layer.shape[0],
              device_error_flag(q.device).data_ptr(), _stream())
     return out
 
@@ -559,7 +566,7 @@ def prefill_key_splits(n_items: int, mean_tiles: float, n_tokens: int, n_heads: 
 def attention_prefill_tc(q: torch.Tensor, cache_layer: torch.Tensor, block_table: torch.Tensor, cu_seqlens: torch.Tensor,
                          positions: torch.Tensor, n_seqs: int, n_long_tokens: int, n_heads: int, n_kv_heads: int,
                          head_dim: int, scale: float, window: "int | None", out: torch.Tensor, min_len: int,
-                         key_splits: int = 1) -> torch.Tensor:
+                         key_splits: int = 1, sink: "float | None" = None) -> torch.Tensor:
     """bfloat16 attention of the entries with at least ``min_len`` tokens on the tcgen05 tensor
     cores (scores and output in tensor memory, Q/K/V tiles by TMA); writes only those entries' rows.
     ``key_splits`` > 1: that many CTAs share the keys of every (query tile, head); a second kernel combines them."""
@@ -585,13 +592,14 @@ def attention_prefill_tc(q: torch.Tensor, cache_layer: torch.Tensor, block_table
         part_ml = torch.empty((q.shape[0], n_heads, key_splits, 2), dtype=torch.float32, device=q.device)
     lib.call("pyre_attention_prefill_tc", q.data_ptr(), cache_layer.data_ptr(), out.data_ptr(), block_table.data_ptr(),
              block_table.stride(0), cu_seqlens.data_ptr(), positions.data_ptr(), q.shape[0], int(n_long_tokens), n_seqs,
-             n_heads, n_kv_heads, head_dim, page_size, cache_layer.shape[0], int(window or 0), float(scale), int(min_len),
+             n_heads, n_kv_heads, head_dim, page_size, cache_layer.shape[0], int(window or 0), float(scale), _sink(sink), int(min_len),
              key_splits, _ptr(part_o), _ptr(part_ml), device_error_flag(q.device).data_ptr(), _stream())
     return out
 
 
 def paged_attention_bf16(ctx, q: torch.Tensor, cache_layer: torch.Tensor, block_table: torch.Tensor, n_heads: int,
-                         n_kv_heads: int, head_dim: int, scale: float, window: "int | None") -> torch.Tensor:
+                         n_kv_heads: int, head_dim: int, scale: float, window: "int | None",
+                         sink: "float | None" = None) -> torch.Tensor:
     """Attention of a whole step in bfloat16: entries with many tokens go to the
     prompt-portion kernel, the others (decoded tokens, short portions) to the split-KV kernel."""
     lens = ctx.cu_seqlens_host[1:] - ctx.cu_seqlens_host[:-1]
@@ -613,10 +621,10 @@ def paged_attention_bf16(ctx, q: torch.Tensor, cache_layer: torch.Tensor, block_
         mean_tiles = float((keys / 64.0 * q_tiles).sum() / q_tiles.sum())
         key_splits = prefill_key_splits(int(q_tiles.sum()) * n_heads, mean_tiles, q.shape[0], n_heads, head_dim)
         attention_prefill_tc(q, cache_layer, block_table, ctx.cu_seqlens, ctx.positions, ctx.num_seqs, n_long, n_heads,
-                             n_kv_heads, head_dim, scale, window, out, min_len, key_splits)
+                             n_kv_heads, head_dim, scale, window, out, min_len, key_splits, sink=sink)
     elif n_long:
         attention_prefill(q, cache_layer, block_table, ctx.cu_seqlens, ctx.positions, ctx.num_seqs, n_long, n_heads,
-                          n_kv_heads, head_dim, scale, window, out)
+                          n_kv_heads, head_dim, scale, window, out, sink=sink)
     if n_short_seqs:
         n_short = ctx.num_tokens - n_long
         short_ctx = int((ctx.start_pos_host + lens)[~long_mask].max())
@@ -626,7 +634,7 @@ def paged_attention_bf16(ctx, q: torch.Tensor, cache_layer: torch.Tensor, block_
         uniform = int(lens[0]) if not n_long and bool((lens == lens[0]).all()) else 0
         paged_attention_mma(q, cache_layer, block_table, ctx.cu_seqlens, ctx.positions, ctx.num_seqs, n_heads,
                             n_kv_heads, head_dim, scale, window, splits, out=out,
-                            max_len=min_len - 1 if n_long else 0, uniform_len=uniform)
+                            max_len=min_len - 1 if n_long else 0, uniform_len=uniform, sink=sink)
     return out
 
 
@@ -1047,3 +1055,192 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, interleaved: bool) ->
     if interleaved and x.dtype == torch.bfloat16 and USE_TC_GEMM and tc_gemm_supported(rows, w_gate_up):
         return gemm_tc(x, w_gate_up, torch.bfloat16, gated=True, checked=True)
     return silu_mul(linear(x, w_gate_up), block=GATED_BLOCK if interleaved else 0)
+
+
+# ---------------------------------------------------------------------------------- layers that are no pre-norm block
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def cast_rows(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """The fp32 residual stream as the activations a branch reads: rounded to ``dtype``; for float32 the stream
+    itself (a branch reads it before the stream is updated)."""
+    _check(x, "x", torch.float32)
+    if dtype == torch.float32:
+        return x
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    lib.call("pyre_cast_rows", x.data_ptr(), out.data_ptr(), x.numel(), _dt(dtype), _stream())
+    return out
+
+
+def norm_add(x: torch.Tensor, y: "torch.Tensor | PartialSums | DeferredProduct", weight: torch.Tensor, eps: float,
+             act_dtype: torch.dtype, want_next: bool = False) -> "torch.Tensor | None":
+    """x[t] += rmsnorm(y[t]) * weight in place on the fp32 stream ``x`` [T, H]: the norm sits on a branch's OUTPUT
+    ``y`` (activation dtype, or fp32 partial sums that the kernel adds).  ``want_next``: also return the new stream
+    as activations (what the next branch reads), written in the same pass."""
+    _check(x, "x", torch.float32, 2)
+    _check(weight, "weight", torch.float32, 1)
+    T, H = x.shape
+    if weight.shape[0] != H:
+        raise ValueError(f"norm weight has {weight.shape[0]} entries, rows have {H}")
+    if isinstance(y, DeferredProduct):
+        y = y.partials()
+    parts, n_parts = None, 0
+    if isinstance(y, PartialSums):
+        parts, n_parts, y = y.parts, y.n, None
+        if tuple(parts.shape[1:]) != (T, H):
+            raise ValueError(f"branch output {tuple(parts.shape[1:])} != stream {(T, H)}")
+    else:
+        _check(y, "y", act_dtype, 2)
+        if tuple(y.shape) != (T, H):
+            raise ValueError(f"branch output {tuple(y.shape)} != stream {(T, H)}")
+    nxt = None
+    if want_next and act_dtype != torch.float32:
+        nxt = torch.empty((T, H), dtype=act_dtype, device=x.device)
+    lib.call("pyre_norm_add", x.data_ptr(), _ptr(y), _ptr(parts), n_parts, T * H, weight.data_ptr(), _ptr(nxt), T, H,
+             float(eps), _dt(act_dtype), _stream())
+    if want_next and nxt is None:
+        return x      # float32 activations are the stream itself
+    return nxt
+
+
+def activation(x: torch.Tensor, kind: str) -> torch.Tensor:
+    """act(x) elementwise, fp32 arithmetic: ``silu`` or ``gelu_tanh`` (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))))."""
+    _check(x, "x")
+    if kind not in ACTIVATIONS:
+        raise UnsupportedSize(f"activation {kind!r}: implemented are {sorted(ACTIVATIONS)}")
+    out = torch.empty_like(x)
+    lib.call("pyre_activation", x.data_ptr(), out.data_ptr(), x.numel(), ACTIVATIONS[kind], _dt(x.dtype), _stream())
+    return out
+
+
+def qk_norm_rope_write(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, q_weight: "torch.Tensor | None",
+                       k_weight: "torch.Tensor | None", eps: float, cos: "torch.Tensor | None", sin: "torch.Tensor | None",
+                       cache_layer: "torch.Tensor | None", slot_mapping: "torch.Tensor | None", n_heads: int,
+                       n_kv_heads: int, qk_dim: int, v_dim: int, row_dim: int, rotary_dim: int, page_size: int) -> torch.Tensor:
+    """Per-head RMS norm of queries and keys (weights [qk_dim], shared by the heads; None: no norm), rotation of
+    the first ``rotary_dim`` dims of each head, and the paged write, for heads whose query/key size ``qk_dim`` and
+    value size ``v_dim`` differ from the cache's row size ``row_dim`` (the rest of a row is zero).
+    ``proj`` [T, W] holds the token's projections: queries at column ``q_col``, keys at ``k_col``, values at ``v_col``.
+    ``cache_layer`` None: nothing is stored and no keys or values are read from ``proj`` (a layer that reads another
+    layer's cache).  Returns the queries [T, n_heads * row_dim]."""
+    _check(proj, "proj", dim=2)
+    T, W = proj.shape
+    D = int(row_dim)
+    write = cache_layer is not None
+    if write:
+        _check(cache_layer, "cache_layer", proj.dtype, 5)
+        if tuple(cache_layer.shape[1:]) != (2, n_kv_heads, page_size, D):
+            raise ValueError(f"cache layer shape {tuple(cache_layer.shape)} does not match [pages, 2, {n_kv_heads}, {page_size}, {D}]")
+        if slot_mapping is None:
+            raise ValueError("slot_mapping is required with a cache")
+        _check(slot_mapping, "slot_mapping", torch.int32, 1)
+        if slot_mapping.shape[0] != T:
+            raise ValueError("slot_mapping must have one entry per token")
+        if k_col < 0 or v_col < 0 or k_col + n_kv_heads * qk_dim > W or v_col + n_kv_heads * v_dim > W:
+            raise ValueError("the keys or values do not lie inside the projection row")
+    if qk_dim > D or v_dim > D:
+        raise ValueError(f"heads of {qk_dim} / {v_dim} do not fit cache rows of {D}")
+    if rotary_dim % 2 or not 0 <= rotary_dim <= qk_dim:
+        raise UnsupportedSize(f"rotary_dim {rotary_dim} must be even and at most the query/key size {qk_dim}")
+    if q_col < 0 or q_col + n_heads * qk_dim > W:
+        raise ValueError("the queries do not lie inside the projection row")
+    for w, name in ((q_weight, "q_weight"), (k_weight, "k_weight")):
+        if w is not None:
+            _check(w, name, torch.float32, 1)
+            if w.shape[0] != qk_dim:
+                raise ValueError(f"{name} has {w.shape[0]} entries, a head has {qk_dim}")
+    half = rotary_dim // 2
+    if rotary_dim:
+        _check(cos, "cos", torch.float32, 2)
+        _check(sin, "sin", torch.float32, 2)
+        if tuple(cos.shape) != (T, half) or tuple(sin.shape) != (T, half):
+            raise ValueError(f"cos/sin must be [{T}, {half}], got {tuple(cos.shape)}")
+    q_out = torch.empty((T, n_heads * D), dtype=proj.dtype, device=proj.device)
+    lib.call("pyre_qk_norm_rope_write", proj.data_ptr(), W, int(q_col), int(k_col) if write else -1, int(v_col) if write else -1,
+             _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(cos) if rotary_dim else None, _ptr(sin) if rotary_dim else None,
+             q_out.data_ptr(), _ptr(cache_layer), _ptr(slot_mapping) if write else None, T, n_heads,
+             n_kv_heads, qk_dim, v_dim, D, rotary_dim, page_size, _dt(proj.dtype),
+             cache_layer.shape[0] if write else 0, device_error_flag(proj.device).data_ptr(), _stream())
+    return q_out
+
+
+def sigmoid_gate(a: torch.Tensor, a_dim: int, proj: "torch.Tensor | None", g_col: int, n_heads: int, v_dim: int) -> torch.Tensor:
+    """out[t, h, j] = a[t, h, j] * sigmoid(proj[t, g_col + h v_dim + j]) for j < v_dim; a head of ``a`` has ``a_dim``
+    columns, of which the first ``v_dim`` count.  ``proj`` None: no gate, the heads are only narrowed.
+    Returns [T, n_heads * v_dim]."""
+    _check(a, "a", dim=2)
+    T = a.shape[0]
+    if a.shape[1] != n_heads * a_dim or a_dim < v_dim:
+        raise ValueError("the heads do not match the tensor")
+    if proj is not None:
+        _check(proj, "proj", a.dtype, 2)
+        if proj.shape[0] != T or g_col < 0 or g_col + n_heads * v_dim > proj.shape[1]:
+            raise ValueError("the gate does not lie inside the projection row")
+    out = torch.empty((T, n_heads * v_dim), dtype=a.dtype, device=a.device)
+    lib.call("pyre_sigmoid_gate", a.data_ptr(), int(a_dim), _ptr(proj), proj.shape[1] if proj is not None else 0,
+             int(g_col) if proj is not None else -1, out.data_ptr(), T, n_heads, v_dim, _dt(a.dtype), _stream())
+    return out
+
+
+def rmsnorm_gate(o: torch.Tensor, weight: torch.Tensor, eps: float, proj: "torch.Tensor | None", g_col: int,
+                 out_dtype: torch.dtype) -> torch.Tensor:
+    """rmsnorm(o[t]) * weight * sigmoid(proj[t, g_col:g_col + H]) over whole rows of fp32 ``o`` [T, H]
+    (``proj`` None: no gate); returns the activation dtype."""
+    _check(o, "o", torch.float32, 2)
+    _check(weight, "weight", torch.float32, 1)
+    T, H = o.shape
+    if weight.shape[0] != H:
+        raise ValueError(f"norm weight has {weight.shape[0]} entries, rows have {H}")
+    if proj is not None:
+        _check(proj, "proj", out_dtype, 2)
+        if proj.shape[0] != T or g_col < 0 or g_col + H > proj.shape[1]:
+            raise ValueError("the gate does not lie inside the projection row")
+    out = torch.empty((T, H), dtype=out_dtype, device=o.device)
+    lib.call("pyre_rmsnorm_gate", o.data_ptr(), weight.data_ptr(), _ptr(proj), proj.shape[1] if proj is not None else 0,
+             int(g_col) if proj is not None else -1, out.data_ptr(), T, H, float(eps), _dt(out_dtype), _stream())
+    return out
+
+
+def linear_attention(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, state_layer: torch.Tensor,
+                     slots: torch.Tensor, cu_seqlens: torch.Tensor, decay: torch.Tensor, n_heads: int, qk_dim: int,
+                     v_dim: int, activation: "str | None" = "silu") -> torch.Tensor:
+    """Linear attention with a constant decay per head over the step's entries, continuing each request's state:
+    S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t, with q, k, v = act(columns of ``proj``).
+    ``state_layer`` [slots, n_heads, qk_dim, v_dim] fp32 is read and left updated at ``slots[b]`` for entry b.
+    Returns fp32 [T, n_heads * v_dim]."""
+    _check(proj, "proj", dim=2)
+    _check(state_layer, "state_layer", torch.float32, 4)
+    _check(slots, "slots", torch.int32, 1)
+    _check(cu_seqlens, "cu_seqlens", torch.int32, 1)
+    _check(decay, "decay", torch.float32, 1)
+    T, W = proj.shape
+    n_seqs = cu_seqlens.shape[0] - 1
+    if tuple(state_layer.shape[1:]) != (n_heads, qk_dim, v_dim) or decay.shape[0] != n_heads or slots.shape[0] < n_seqs:
+        raise ValueError("state, decay or slots do not match the heads and the batch")
+    if qk_dim > 256:
+        raise UnsupportedSize(f"linear attention takes query/key sizes up to 256, got {qk_dim}")
+    if min(q_col, k_col, v_col) < 0 or max(q_col, k_col) + n_heads * qk_dim > W or v_col + n_heads * v_dim > W:
+        raise ValueError("q, k or v do not lie inside the projection row")
+    if activation not in (None, "silu"):
+        raise UnsupportedSize(f"linear attention: activation {activation!r} is not implemented")
+    out = torch.empty((T, n_heads * v_dim), dtype=torch.float32, device=proj.device)
+    lib.call("pyre_linear_attention_scan", proj.data_ptr(), W, int(q_col), int(k_col), int(v_col), state_layer.data_ptr(),
+             slots.data_ptr(), cu_seqlens.data_ptr(), decay.data_ptr(), out.data_ptr(), T, n_seqs, n_heads, qk_dim, v_dim,
+             1 if activation == "silu" else 0, _dt(proj.dtype), _stream())
+    return out
+
+
+def attention_row_dim(qk_dim: int, v_dim: int, dtype: torch.dtype) -> int:
+    """The row size of a paged cache whose heads have ``qk_dim`` query/key dims and ``v_dim`` value dims: one size
+    for keys and values, so that every attention kernel of the package serves them (the columns beyond a head's own
+    are zero and change neither scores nor outputs).  A multiple of 16; for bfloat16 the head sizes of the
+    prompt-portion kernels (64, 128) where the heads are larger than 32."""
+    d = -(-max(int(qk_dim), int(v_dim)) // 16) * 16
+    if dtype == torch.bfloat16:
+        if 32 < d <= 64:
+            d = 64
+        elif 64 < d <= 128:
+            d = 128
+    if d > 256:
+        raise UnsupportedSize(f"heads of {qk_dim} / {v_dim} dims: the attention kernels take up to 256")
+    return d

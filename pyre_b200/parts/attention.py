@@ -7,7 +7,7 @@ import torch
 
 from ..kernels import lib, ops
 from ..weights.specs import TensorSpec
-from .base import HeadGeometry, PagedKVSpec, Part, PartSpec, make_part, register_part
+from .base import HeadGeometry, PagedKVSpec, Part, PartSpec, ProjectionLayout, make_part, register_part
 
 
 class Attention(Part):
@@ -22,22 +22,46 @@ class Attention(Part):
     names of the four projections (default q_proj, k_proj, v_proj, o_proj: an architecture whose checkpoint
     calls them otherwise says so in its builder, no new part needed).
     A query at position p sees keys max(0, p - window + 1)..p.
+
+    Further parameters, all off by default (the stacked, fused path above is untouched by them):
+    ``v_head_dim``: a value head's size when it differs from ``head_dim`` (the cache's rows then have one size that
+    holds both, ``ops.attention_row_dim``, the rest zero);
+    ``qk_norm``: an RMS norm per head over the ``head_dim`` dims of queries and keys before the position encoding,
+    ``{"eps": e}``, with weights of ``head_dim`` entries shared by the heads (names ``q_norm`` / ``k_norm``);
+    ``sink``: the score of a sink that has no value: exp(sink) joins every softmax denominator;
+    ``out_gate``: the concatenated heads are multiplied by sigmoid(W_g h) before the output projection (name ``g``);
+    ``own_kv=False``: the mixer has no key and value projections (and no key norm): it reads the cache layer that
+    another entry of the schedule writes (``LayerCall(cache=..., write=False)``);
+    ``weight_suffix``: what follows a projection's name in the checkpoint (".weight").
     """
 
-    DEFAULT_NAMES = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj"}
+    DEFAULT_NAMES = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj", "g": "g_proj", "q_norm": "q_norm.weight",
+                     "k_norm": "k_norm.weight"}
 
     graph_safe = True
     takes_scaled_rows = True      # ``h`` may be ``ops.ScaledRows``: the q/k/v product applies the norm's 1/rms itself
 
     def __init__(self, dtype, device, width: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  position: "PartSpec | None" = None, qkv_bias: bool = True, o_bias: bool = False,
-                 scale: "float | None" = None, window: "int | None" = None, names: "dict[str, str] | None" = None):
+                 scale: "float | None" = None, window: "int | None" = None, names: "dict[str, str] | None" = None,
+                 v_head_dim: "int | None" = None, qk_norm: "dict | None" = None, sink: "float | None" = None,
+                 out_gate: bool = False, own_kv: bool = True, weight_suffix: str = ".weight"):
         super().__init__(dtype, device)
+        self.v_head_dim = int(v_head_dim) if v_head_dim is not None else int(head_dim)
+        self.qk_norm_eps = float(qk_norm["eps"]) if qk_norm is not None else None
+        self.sink = float(sink) if sink is not None else None
+        self.out_gate, self.own_kv, self.suffix = bool(out_gate), bool(own_kv), str(weight_suffix)
+        # the general path: projections laid out by a ProjectionLayout, unfused small kernels
+        self.general = self.v_head_dim != int(head_dim) or qk_norm is not None or self.out_gate or not self.own_kv
+        if self.general and qkv_bias:
+            raise ops.UnsupportedSize("projection biases together with v_head_dim, qk_norm, out_gate or own_kv=False are not implemented")
         self.names = dict(self.DEFAULT_NAMES, **(names or {}))
         self.width, self.n_heads, self.n_kv_heads, self.head_dim = int(width), int(n_heads), int(n_kv_heads), int(head_dim)
         if self.n_heads % self.n_kv_heads:
             raise ops.UnsupportedSize(f"{n_heads} query heads cannot be shared among {n_kv_heads} key/value heads")
-        if self.head_dim % 16 or not 16 <= self.head_dim <= 256:
+        # the size of a cache row: the head size itself, or (general path) one size that holds keys and values
+        self.row_dim = ops.attention_row_dim(self.head_dim, self.v_head_dim, dtype) if self.general else self.head_dim
+        if self.row_dim % 16 or not 16 <= self.row_dim <= 256:
             raise ops.UnsupportedSize(f"head_dim {head_dim}: the attention kernels take multiples of 16 from 16 to 256")
         if o_bias:
             raise ops.UnsupportedSize("an output-projection bias is not implemented")
@@ -49,6 +73,11 @@ class Attention(Part):
         self.heads = HeadGeometry(self.n_heads, self.n_kv_heads, self.head_dim)
         self.position = make_part("position", position or PartSpec("none"), dtype, device)
         self.w_qkv = self.b_qkv = self.w_o = None
+        self.w_proj = self.q_norm_w = self.k_norm_w = None
+        q_cols, kv_cols = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim
+        self.layout = ProjectionLayout(self.n_heads, self.n_kv_heads, self.head_dim, self.v_head_dim, self.row_dim, 0,
+                                       q_cols if self.own_kv else -1, q_cols + kv_cols if self.own_kv else -1)
+        self.g_col = q_cols + (kv_cols + self.n_kv_heads * self.v_head_dim if self.own_kv else 0)
 
     def children(self):
         # a position encoding with tensors of its own would find them under the mixer's prefix
@@ -58,6 +87,21 @@ class Attention(Part):
         q, kv = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim
         n = self.names
         t = {}
+        if self.general:
+            sfx = self.suffix
+            vq, vkv = self.n_heads * self.v_head_dim, self.n_kv_heads * self.v_head_dim
+            t[n["q"] + sfx] = TensorSpec((q, self.width))
+            if self.own_kv:
+                t[n["k"] + sfx] = TensorSpec((kv, self.width))
+                t[n["v"] + sfx] = TensorSpec((vkv, self.width))
+            if self.qk_norm_eps is not None:
+                t[n["q_norm"]] = TensorSpec((self.head_dim,), role="vector", init=("normal", 1.0, 0.1))
+                if self.own_kv:
+                    t[n["k_norm"]] = TensorSpec((self.head_dim,), role="vector", init=("normal", 1.0, 0.1))
+            if self.out_gate:
+                t[n["g"] + sfx] = TensorSpec((vq, self.width))
+            t[n["o"] + sfx] = TensorSpec((self.width, vq))
+            return t
         # checkpoint order: weight then bias per projection, the output projection last
         for key, rows in (("q", q), ("k", kv), ("v", kv)):
             t[f"{n[key]}.weight"] = TensorSpec((rows, self.width))
@@ -68,6 +112,17 @@ class Attention(Part):
 
     def load(self, tensors):
         n = self.names
+        if self.general:
+            sfx = self.suffix
+            stack = [tensors[n["q"] + sfx]] + ([tensors[n["k"] + sfx], tensors[n["v"] + sfx]] if self.own_kv else [])
+            if self.out_gate:
+                stack.append(tensors[n["g"] + sfx])
+            self.w_proj = torch.cat(stack, dim=0).contiguous() if len(stack) > 1 else stack[0]
+            if self.qk_norm_eps is not None:
+                self.q_norm_w = tensors[n["q_norm"]]
+                self.k_norm_w = tensors[n["k_norm"]] if self.own_kv else None
+            self.w_o = tensors[n["o"] + sfx]
+            return
         self.w_qkv = torch.cat([tensors[f"{n[k]}.weight"] for k in "qkv"], dim=0).contiguous()
         if self.qkv_bias:
             self.b_qkv = torch.cat([tensors[f"{n[k]}.bias"] for k in "qkv"]).contiguous()
@@ -75,9 +130,11 @@ class Attention(Part):
 
     def kernel_libraries(self):
         libs = ["elementwise"]      # the position encoding, a sub-part, names its own
-        if self.dtype == torch.bfloat16 and self.head_dim <= ops.MMA_MAX_HEAD_DIM:
+        if self.general:
+            libs.append("blockops")
+        if self.dtype == torch.bfloat16 and self.row_dim <= ops.MMA_MAX_HEAD_DIM:
             libs.append("attention_mma")
-            if self.head_dim in ops.PREFILL_HEAD_DIMS:
+            if self.row_dim in ops.PREFILL_HEAD_DIMS:
                 libs += ["attention_prefill", "attention_tc"]
         else:
             libs.append("attention_generic")
@@ -85,7 +142,7 @@ class Attention(Part):
         return libs
 
     def cache_spec(self):
-        return PagedKVSpec(self.n_kv_heads, self.head_dim, self.window)
+        return PagedKVSpec(self.n_kv_heads, self.row_dim, self.window)
 
     def state_spec(self):
         return None
@@ -94,7 +151,34 @@ class Attention(Part):
         # the tensor-core kernel's split count is chosen on the host from these numbers
         return (ops.attention_splits(n_rows, n_rows, self.n_heads, self.n_kv_heads, max_context, self.window),)
 
+    def _attend(self, ctx, q, layer, kv):
+        if self.dtype == torch.bfloat16 and self.row_dim <= ops.MMA_MAX_HEAD_DIM:
+            return ops.paged_attention_bf16(ctx, q, layer, kv.block_table, self.n_heads, self.n_kv_heads, self.row_dim,
+                                            self.scale, self.window, sink=self.sink)
+        # float32 and head sizes above 128: the exact fp32-arithmetic kernel
+        return ops.paged_attention_generic(q, layer, kv.block_table, ctx.seq_of_token, ctx.positions, self.n_heads,
+                                           self.n_kv_heads, self.row_dim, self.scale, self.window, sink=self.sink)
+
+    def _forward_general(self, ctx, h, call):
+        """Projections in one product [q | k | v | gate]; norm, position encoding and the paged write by the
+        encoding's ``apply_layout``; attention over cache rows of ``row_dim``; the gate; the output projection."""
+        kv = ctx.kv_group(call.kv_group)
+        layer = kv.pool[call.kv_layer]
+        if self.own_kv != bool(call.kv_write):
+            raise ValueError("a mixer with its own keys and values writes its cache layer; one without reads another's")
+        with lib.section("qkv"):
+            proj = ops.materialize(ops.linear(h, self.w_proj))
+        q = self.position.apply_layout(ctx, proj, self.layout, self.q_norm_w, self.k_norm_w, self.qk_norm_eps or 0.0, kv,
+                                       layer if call.kv_write else None)
+        a = self._attend(ctx, q, layer, kv)
+        if self.out_gate or self.row_dim != self.v_head_dim:
+            a = ops.sigmoid_gate(a, self.row_dim, proj if self.out_gate else None, self.g_col, self.n_heads, self.v_head_dim)
+        with lib.section("o"):
+            return ops.linear(a, self.w_o, partials_ok=True)
+
     def forward(self, ctx, h, call):
+        if self.general:
+            return self._forward_general(ctx, h, call)
         kv = ctx.kv_group(call.kv_group)
         layer = kv.pool[call.kv_layer]
         with lib.section("qkv"):
@@ -102,13 +186,7 @@ class Attention(Part):
         # the position encoding owns the step from projections to cache: bias, its transformation of q and k,
         # the paged write of k and v; the queries come back
         q = self.position.apply(ctx, qkv, self.b_qkv, self.heads, kv, layer if call.kv_write else None)
-        if self.dtype == torch.bfloat16 and self.head_dim <= ops.MMA_MAX_HEAD_DIM:
-            a = ops.paged_attention_bf16(ctx, q, layer, kv.block_table, self.n_heads, self.n_kv_heads, self.head_dim,
-                                         self.scale, self.window)
-        else:
-            # float32 and head sizes above 128: the exact fp32-arithmetic kernel
-            a = ops.paged_attention_generic(q, layer, kv.block_table, ctx.seq_of_token, ctx.positions, self.n_heads,
-                                            self.n_kv_heads, self.head_dim, self.scale, self.window)
+        a = self._attend(ctx, q, layer, kv)
         with lib.section("o"):
             return ops.linear(a, self.w_o, partials_ok=True, deferred_ok="residual")
 

@@ -117,6 +117,23 @@ class HeadGeometry:
 
 
 @dataclass(frozen=True)
+class ProjectionLayout:
+    """Where a token's queries, keys and values lie in a row of stacked projections when a head's query/key size
+    ``qk_dim`` and value size ``v_dim`` are not the cache's row size ``row_dim`` (>= both): ``n_heads`` query heads
+    from column ``q_col``, ``n_kv_heads`` key heads from ``k_col`` and as many value heads from ``v_col``
+    (``k_col`` < 0: the row holds no keys or values).  The row may hold more columns (a gate)."""
+
+    n_heads: int
+    n_kv_heads: int
+    qk_dim: int
+    v_dim: int
+    row_dim: int
+    q_col: int = 0
+    k_col: int = -1
+    v_col: int = -1
+
+
+@dataclass(frozen=True)
 class BoundCall:
     """One entry of the layer schedule, resolved against the cache manager's groups."""
 
@@ -172,6 +189,23 @@ class PositionEncoding(Part):
     def apply(self, ctx, qkv, bias, heads: HeadGeometry, kv, cache_layer):
         """No encoding at all: bias added, keys and values stored as projected."""
         return self.store(qkv, bias, heads, kv, cache_layer)
+
+    def rotation(self, ctx, qk_dim: int):
+        """(cos, sin, rotary_dim) of the step's tokens for heads of ``qk_dim`` dims, or (None, None, 0) for an
+        encoding that does not rotate.  Used by ``apply_layout``."""
+        return None, None, 0
+
+    def apply_layout(self, ctx, proj, layout: ProjectionLayout, q_norm, k_norm, norm_eps: float, kv, cache_layer):
+        """The same step for projections laid out by a ``ProjectionLayout`` (key and value sizes that differ, rows
+        padded to the cache's row size), with an optional RMS norm per head over the query and key dims before
+        the encoding (``q_norm`` / ``k_norm``: fp32 weights [qk_dim] or None).  Stores keys and values in
+        ``cache_layer`` (None: nothing) and returns the queries [T, n_heads * row_dim].  An encoding that is a
+        rotation of leading dims only has to give ``rotation``."""
+        from ..kernels import ops
+        cos, sin, rotary_dim = self.rotation(ctx, layout.qk_dim)
+        return ops.qk_norm_rope_write(proj, layout.q_col, layout.k_col, layout.v_col, q_norm, k_norm, norm_eps, cos, sin,
+                                      cache_layer, kv.slot_mapping, layout.n_heads, layout.n_kv_heads, layout.qk_dim,
+                                      layout.v_dim, layout.row_dim, rotary_dim, kv.page_size)
 
     @staticmethod
     def store(qkv, bias, heads: HeadGeometry, kv, cache_layer):

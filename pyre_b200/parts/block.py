@@ -1,4 +1,5 @@
-"""Arrangement of a layer's parts: the pre-norm residual block (pyre/model.py:142-153)."""
+"""Arrangements of a layer's parts: the pre-norm residual block (pyre/model.py:142-153), and a block whose norms
+sit on the branches' outputs."""
 
 from __future__ import annotations
 
@@ -49,3 +50,59 @@ class PreNormBlock(Part):
 
 
 register_part("block", "prenorm", PreNormBlock)
+
+
+class OutputNormBlock(Part):
+    """x = x + norm1(mixer(x)); x = x + norm2(ffn(x)): the norms sit on the branches' OUTPUTS and the branches
+    read the stream itself.  ``norm2`` and ``ffn`` may both be None: a layer with one branch.
+
+    The residual stream ``x`` is fp32 and is updated in place by the norm's kernel, which also leaves the new
+    stream as activations for the branch that reads it next (one pass over the row); the block therefore never
+    leaves anything pending.  A branch output still pending from a block before it is added first.
+
+    ``names`` gives the prefix of each sub-part's tensors inside the layer."""
+
+    graph_safe = True
+
+    DEFAULT_NAMES = {"norm1": "norm1.", "mixer": "mixer.", "norm2": "norm2.", "ffn": "ffn."}
+    _STREAM = "stream_as_activations"      # ctx.scratch: (the stream tensor, its activations) left by the last norm
+
+    def __init__(self, dtype, device, norm1: PartSpec, mixer: PartSpec, norm2: "PartSpec | None" = None,
+                 ffn: "PartSpec | None" = None, names: "dict[str, str] | None" = None):
+        super().__init__(dtype, device)
+        if (norm2 is None) != (ffn is None):
+            raise ValueError("a second branch needs both its norm and its feed-forward")
+        self.names = dict(self.DEFAULT_NAMES, **(names or {}))
+        self.norm1 = make_part("norm", norm1, dtype, device)
+        self.mixer = make_part("mixer", mixer, dtype, device)
+        self.norm2 = make_part("norm", norm2, dtype, device) if norm2 is not None else None
+        self.ffn = make_part("ffn", ffn, dtype, device) if ffn is not None else None
+        for n in (self.norm1, self.norm2):
+            if n is not None and not hasattr(n, "add_normed"):
+                raise ValueError(f"{type(n).__name__} cannot sit on a branch's output: it has no add_normed")
+
+    def children(self):
+        out = {self.names["norm1"]: self.norm1, self.names["mixer"]: self.mixer}
+        if self.ffn is not None:
+            out[self.names["norm2"]] = self.norm2
+            out[self.names["ffn"]] = self.ffn
+        return out
+
+    def kernel_libraries(self):
+        return ["elementwise", "blockops"]
+
+    def forward(self, ctx, x, pending, call):
+        from ..kernels import ops
+        left = ctx.scratch.pop(self._STREAM, None)
+        if pending is not None:
+            ops.add_residual(x, ops.materialize(pending))
+            left = None
+        h = left[1] if left is not None and left[0] is x else ops.cast_rows(x, self.dtype)
+        h = self.norm1.add_normed(ctx, x, self.mixer.forward(ctx, h, call), want_next=True)
+        if self.ffn is not None:
+            h = self.norm2.add_normed(ctx, x, self.ffn.forward(ctx, h), want_next=True)
+        ctx.scratch[self._STREAM] = (x, h)
+        return x, None
+
+
+register_part("block", "output_norm", OutputNormBlock)

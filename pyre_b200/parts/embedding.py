@@ -14,16 +14,16 @@ class TokenEmbedding(Part):
 
     graph_safe = True
 
-    def __init__(self, dtype, device, vocab: int, width: int):
+    def __init__(self, dtype, device, vocab: int, width: int, tensor_name: str = "weight"):
         super().__init__(dtype, device)
-        self.vocab, self.width = int(vocab), int(width)
+        self.vocab, self.width, self.tensor_name = int(vocab), int(width), str(tensor_name)
         self.table = None
 
     def tensors(self):
-        return {"weight": TensorSpec((self.vocab, self.width))}
+        return {self.tensor_name: TensorSpec((self.vocab, self.width))}
 
     def load(self, tensors):
-        self.table = tensors["weight"]
+        self.table = tensors[self.tensor_name]
 
     def kernel_libraries(self):
         return ["elementwise"]
@@ -40,16 +40,16 @@ class LinearHead(Part):
 
     graph_safe = True
 
-    def __init__(self, dtype, device, vocab: int, width: int, tied_to: "str | None" = None):
+    def __init__(self, dtype, device, vocab: int, width: int, tied_to: "str | None" = None, tensor_name: str = "weight"):
         super().__init__(dtype, device)
-        self.vocab, self.width, self.tied_to = int(vocab), int(width), tied_to
+        self.vocab, self.width, self.tied_to, self.tensor_name = int(vocab), int(width), tied_to, str(tensor_name)
         self.weight = None
 
     def tensors(self):
-        return {"weight": TensorSpec((self.vocab, self.width), optional_alias=self.tied_to)}
+        return {self.tensor_name: TensorSpec((self.vocab, self.width), optional_alias=self.tied_to)}
 
     def load(self, tensors):
-        self.weight = tensors["weight"]
+        self.weight = tensors[self.tensor_name]
 
     def kernel_libraries(self):
         return ["gemm_f32"] if self.dtype == torch.float32 else ["gemm_tc"]

@@ -1,4 +1,4 @@
-"""Dense gated feed-forward (SwiGLU, pyre/model.py:128-139)."""
+"""Dense feed-forwards: the gated one (SwiGLU, pyre/model.py:128-139) and the plain one (up, activation, down)."""
 
 from __future__ import annotations
 
@@ -59,3 +59,43 @@ class GatedMLP(Part):
 
 
 register_part("ffn", "gated_mlp", GatedMLP)
+
+
+class DenseMLP(Part):
+    """down(act(up(h))) without biases: a feed-forward with one product before the activation.
+    ``activation``: ``gelu_tanh`` (0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))) or ``silu``, computed in fp32
+    on the product's result.  ``names``: the checkpoint's full local names of the two weights."""
+
+    DEFAULT_NAMES = {"up": "up_proj.weight", "down": "down_proj.weight"}
+
+    graph_safe = True
+
+    def __init__(self, dtype, device, width: int, intermediate: int, activation: str = "gelu_tanh",
+                 names: "dict[str, str] | None" = None):
+        super().__init__(dtype, device)
+        self.names = dict(self.DEFAULT_NAMES, **(names or {}))
+        self.width, self.intermediate = int(width), int(intermediate)
+        if activation not in ops.ACTIVATIONS:
+            raise ops.UnsupportedSize(f"activation {activation!r}: implemented are {sorted(ops.ACTIVATIONS)}")
+        self.activation = activation
+        self.w_up = self.w_down = None
+
+    def tensors(self):
+        return {self.names["up"]: TensorSpec((self.intermediate, self.width)),
+                self.names["down"]: TensorSpec((self.width, self.intermediate))}
+
+    def load(self, tensors):
+        self.w_up, self.w_down = tensors[self.names["up"]], tensors[self.names["down"]]
+
+    def kernel_libraries(self):
+        return ["blockops", "elementwise"] + (["gemm_f32"] if self.dtype == torch.float32 else ["gemm_tc"])
+
+    def forward(self, ctx, h):
+        with lib.section("up"):
+            z = ops.linear(h, self.w_up)
+        a = ops.activation(z, self.activation)
+        with lib.section("down"):
+            return ops.linear(a, self.w_down, partials_ok=True)
+
+
+register_part("ffn", "dense_mlp", DenseMLP)

@@ -8,29 +8,40 @@ from .base import Part, register_part
 
 
 class RMSNorm(Part):
-    """h = (v / sqrt(mean(v^2) + eps)) * weight with v = x + delta, all in fp32; ``x`` is
-    the fp32 residual stream and receives the sum."""
+    """h = (v / sqrt(mean(v^2) + eps)) * gain with v = x + delta, all in fp32; ``x`` is
+    the fp32 residual stream and receives the sum.
+
+    ``offset``: the checkpoint stores ``gain - offset`` (a weight kept around zero has offset 1; the sum is
+    formed once, in fp32, at load).  ``tensor_name``: the local name of the weight ("" when the prefix is the
+    whole name).  Beside the pre-norm use (``forward``) the same norm can sit on a branch's output:
+    ``add_normed`` adds norm(y) * gain to the stream."""
 
     graph_safe = True
     fuses_into_product = True     # forward takes ``scaled_ok``: with it, the norm may run as the fix-up of the product
                                   # that ``delta`` stands for and hand its consumer ``ops.ScaledRows``
 
-    def __init__(self, dtype, device, width: int, eps: float):
+    def __init__(self, dtype, device, width: int, eps: float, offset: float = 0.0, tensor_name: str = "weight"):
         super().__init__(dtype, device)
-        self.width, self.eps = int(width), float(eps)
+        self.width, self.eps, self.offset, self.tensor_name = int(width), float(eps), float(offset), str(tensor_name)
         self.weight = None
 
     def tensors(self):
-        return {"weight": TensorSpec((self.width,), role="vector", init=("normal", 1.0, 0.1))}
+        return {self.tensor_name: TensorSpec((self.width,), role="vector", init=("normal", 1.0 - self.offset, 0.1))}
 
     def load(self, tensors):
-        self.weight = tensors["weight"]
+        w = tensors[self.tensor_name]
+        self.weight = w + self.offset if self.offset else w
 
     def kernel_libraries(self):
         return ["elementwise"]
 
     def forward(self, ctx, x, delta=None, rows=None, update_x=True, scaled_ok=False):
         return ops.add_rmsnorm(x, delta, self.weight, self.eps, self.dtype, rows=rows, update_x=update_x, scaled_ok=scaled_ok)
+
+    def add_normed(self, ctx, x, y, want_next: bool = False):
+        """x += norm(y) * gain on the fp32 stream, ``y`` a branch's output; with ``want_next`` the new stream comes
+        back as activations for the branch that reads it next."""
+        return ops.norm_add(x, y, self.weight, self.eps, self.dtype, want_next=want_next)
 
 
 register_part("norm", "rms_norm", RMSNorm)

@@ -19,18 +19,22 @@ class Rotary(PositionEncoding):
     graph_safe = True
 
     def __init__(self, dtype, device, head_dim: int, theta: float, rotary_dim: "int | None" = None,
-                 pairing: str = "half"):
+                 pairing: str = "half", exact_frequencies: bool = False):
         super().__init__(dtype, device)
         self.head_dim = int(head_dim)
         self.rotary_dim = int(rotary_dim if rotary_dim is not None else head_dim)
         self.theta = float(theta)
         if pairing != "half":
             raise ops.UnsupportedSize(f"rotary pairing {pairing!r}: only the half-split pairing is implemented")
-        if self.rotary_dim % 8 or self.rotary_dim > self.head_dim:
-            raise ops.UnsupportedSize(f"rotary_dim {self.rotary_dim} must be a multiple of 8 and <= head_dim")
-        inv = 1.0 / (self.theta ** (torch.arange(0, self.rotary_dim, 2, dtype=torch.float32) / self.rotary_dim))
+        if self.rotary_dim % 2 or self.rotary_dim > self.head_dim:
+            raise ops.UnsupportedSize(f"rotary_dim {self.rotary_dim} must be even and <= head_dim")
+        if exact_frequencies:
+            # theta^(-2j / rotary_dim) in 64-bit, rounded once to fp32
+            inv = (self.theta ** (-torch.arange(0, self.rotary_dim, 2, dtype=torch.float64) / self.rotary_dim)).float()
+        else:
+            inv = 1.0 / (self.theta ** (torch.arange(0, self.rotary_dim, 2, dtype=torch.float32) / self.rotary_dim))
         self.inv_freq = inv.to(self.device)
-        self._key = ("rotary", self.rotary_dim, self.theta)
+        self._key = ("rotary", self.rotary_dim, self.theta, bool(exact_frequencies))
 
     def kernel_libraries(self):
         return ["elementwise"]
@@ -42,6 +46,12 @@ class Rotary(PositionEncoding):
             ctx.scratch[self._key] = tab
         return tab
 
+
+    def rotation(self, ctx, qk_dim: int):
+        if qk_dim != self.head_dim:
+            raise ValueError(f"rotary part built for head_dim {self.head_dim}, used with {qk_dim}")
+        cos, sin = self.tables(ctx)
+        return cos, sin, self.rotary_dim
 
     def apply(self, ctx, qkv, bias, heads: HeadGeometry, kv, cache_layer):
         if heads.head_dim != self.head_dim:

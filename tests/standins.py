@@ -62,7 +62,7 @@ def qkv_rope_write(qkv, bias, cos, sin, cache_layer, slot_mapping, n_heads, n_kv
 
 
 def paged_attention_generic(q, cache_layer, block_table, seq_of_token, positions, n_heads, n_kv_heads, head_dim, scale,
-                            window=None, out=None):
+                            window=None, out=None, sink=None):
     T = q.shape[0]
     page_size = cache_layer.shape[3]
     n_rep = n_heads // n_kv_heads
@@ -77,9 +77,94 @@ def paged_attention_generic(q, cache_layer, block_table, seq_of_token, positions
         vals = cache_layer[pages, 1, :, pos % page_size, :].float()
         qt = q[t].float().reshape(n_kv_heads, n_rep, head_dim)
         scores = torch.einsum("grd,kgd->grk", qt, keys) * scale
-        probs = torch.softmax(scores, dim=-1)
+        if sink is None:
+            probs = torch.softmax(scores, dim=-1)
+        else:       # one more term in the denominator, with no value
+            top = scores.max(dim=-1, keepdim=True).values.clamp_min(sink)
+            e = torch.exp(scores - top)
+            probs = e / (e.sum(dim=-1, keepdim=True) + torch.exp(sink - top))
         result[t] = torch.einsum("grk,kgd->grd", probs, vals).reshape(-1).to(q.dtype)
     return result
+
+
+def cast_rows(x, dtype):
+    return x if dtype == torch.float32 else x.to(dtype)
+
+
+def norm_add(x, y, weight, eps, act_dtype, want_next=False):
+    v = _partial_sums_or_tensor(y)
+    x.add_(v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * weight)
+    if not want_next:
+        return None
+    return x if act_dtype == torch.float32 else x.to(act_dtype)
+
+
+def activation(x, kind):
+    z = x.float()
+    if kind == "silu":
+        return torch.nn.functional.silu(z).to(x.dtype)
+    assert kind == "gelu_tanh"
+    return torch.nn.functional.gelu(z, approximate="tanh").to(x.dtype)
+
+
+def qk_norm_rope_write(proj, q_col, k_col, v_col, q_weight, k_weight, eps, cos, sin, cache_layer, slot_mapping, n_heads,
+                       n_kv_heads, qk_dim, v_dim, row_dim, rotary_dim, page_size):
+    T = proj.shape[0]
+    x = proj.float()
+
+    def heads(col, n, d, w):
+        t = x[:, col:col + n * d].reshape(T, n, d)
+        if w is not None:
+            t = t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + eps) * w
+        if rotary_dim:
+            half = rotary_dim // 2
+            a, b, rest = t[..., :half], t[..., half:rotary_dim], t[..., rotary_dim:]
+            c, s = cos[:, None, :], sin[:, None, :]
+            t = torch.cat([a * c - b * s, b * c + a * s, rest], dim=-1)
+        return torch.nn.functional.pad(t, (0, row_dim - d))
+
+    q = heads(q_col, n_heads, qk_dim, q_weight)
+    if cache_layer is not None:
+        k = heads(k_col, n_kv_heads, qk_dim, k_weight)
+        v = torch.nn.functional.pad(x[:, v_col:v_col + n_kv_heads * v_dim].reshape(T, n_kv_heads, v_dim), (0, row_dim - v_dim))
+        for t in range(T):
+            page, off = divmod(int(slot_mapping[t]), page_size)
+            cache_layer[page, 0, :, off, :] = k[t].to(cache_layer.dtype)
+            cache_layer[page, 1, :, off, :] = v[t].to(cache_layer.dtype)
+    return q.reshape(T, n_heads * row_dim).to(proj.dtype)
+
+
+def sigmoid_gate(a, a_dim, proj, g_col, n_heads, v_dim):
+    T = a.shape[0]
+    out = a.float().reshape(T, n_heads, a_dim)[..., :v_dim].reshape(T, n_heads * v_dim)
+    if proj is not None:
+        out = out * torch.sigmoid(proj[:, g_col:g_col + n_heads * v_dim].float())
+    return out.to(a.dtype)
+
+
+def rmsnorm_gate(o, weight, eps, proj, g_col, out_dtype):
+    v = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps) * weight
+    if proj is not None:
+        v = v * torch.sigmoid(proj[:, g_col:g_col + o.shape[1]].float())
+    return v.to(out_dtype)
+
+
+def linear_attention(proj, q_col, k_col, v_col, state_layer, slots, cu_seqlens, decay, n_heads, qk_dim, v_dim,
+                     activation="silu"):
+    T = proj.shape[0]
+    x = proj.float()
+    act = torch.nn.functional.silu if activation == "silu" else (lambda z: z)
+    q = act(x[:, q_col:q_col + n_heads * qk_dim]).reshape(T, n_heads, qk_dim)
+    k = act(x[:, k_col:k_col + n_heads * qk_dim]).reshape(T, n_heads, qk_dim)
+    v = act(x[:, v_col:v_col + n_heads * v_dim]).reshape(T, n_heads, v_dim)
+    out = torch.empty((T, n_heads, v_dim), dtype=torch.float32)
+    cu = cu_seqlens.tolist()
+    for b in range(len(cu) - 1):
+        S = state_layer[int(slots[b])]            # [heads, qk_dim, v_dim], updated in place
+        for t in range(cu[b], cu[b + 1]):
+            S.mul_(decay[:, None, None]).add_(k[t][:, :, None] * v[t][:, None, :])
+            out[t] = torch.einsum("hkv,hk->hv", S, q[t])
+    return out.reshape(T, n_heads * v_dim)
 
 
 def sgemm_nt(a, w, bias=None, out=None):
@@ -113,7 +198,9 @@ def install(monkeypatch) -> None:
     flag = torch.zeros(1, dtype=torch.int32)
     for name, fn in dict(embedding=embedding, add_rmsnorm=add_rmsnorm, add_residual=add_residual, rope_table=rope_table,
                          qkv_rope_write=qkv_rope_write, paged_attention_generic=paged_attention_generic,
-                         sgemm_nt=sgemm_nt, silu_mul=silu_mul, sample=sample, feed_tokens=feed_tokens).items():
+                         sgemm_nt=sgemm_nt, silu_mul=silu_mul, sample=sample, feed_tokens=feed_tokens, cast_rows=cast_rows,
+                         norm_add=norm_add, activation=activation, qk_norm_rope_write=qk_norm_rope_write,
+                         sigmoid_gate=sigmoid_gate, rmsnorm_gate=rmsnorm_gate, linear_attention=linear_attention).items():
         monkeypatch.setattr(ops, name, fn)
     monkeypatch.setattr(ops, "device_error_flag", lambda device: flag)
     monkeypatch.setattr(ops, "check_device_errors", lambda device="cpu": None)
