@@ -270,7 +270,7 @@ def silu_mul_any(gate_up, out=None, block=0):
 
 
 def _attend_entries(q, cache_layer, block_table, cu_seqlens, positions, n_seqs, n_heads, n_kv_heads, head_dim, scale, window,
-                    out, takes):
+                    out, takes, sink=None):
     cu = cu_seqlens.tolist()
     taken = 0
     for b in range(n_seqs):
@@ -280,12 +280,12 @@ def _attend_entries(q, cache_layer, block_table, cu_seqlens, positions, n_seqs, 
         taken += n
         rows = slice(cu[b], cu[b + 1])
         out[rows] = paged_attention_generic(q[rows], cache_layer, block_table[b:b + 1], torch.zeros(n, dtype=torch.int32),
-                                            positions[rows], n_heads, n_kv_heads, head_dim, scale, window)
+                                            positions[rows], n_heads, n_kv_heads, head_dim, scale, window, sink=sink)
     return taken
 
 
 def paged_attention_mma(q, cache_layer, block_table, cu_seqlens, positions, n_seqs, n_heads, n_kv_heads, head_dim, scale,
-                        window=None, n_splits=1, out=None, scratch=None, max_len=0, uniform_len=0):
+                        window=None, n_splits=1, out=None, scratch=None, max_len=0, uniform_len=0, sink=None):
     from pyre_b200.kernels import ops
     assert q.dtype == cache_layer.dtype == torch.bfloat16 and head_dim <= ops.MMA_MAX_HEAD_DIM
     assert 1 <= n_splits <= ops.MAX_SCRATCH_SPLITS
@@ -294,27 +294,27 @@ def paged_attention_mma(q, cache_layer, block_table, cu_seqlens, positions, n_se
     if out is None:
         out = torch.empty_like(q)
     _attend_entries(q, cache_layer, block_table, cu_seqlens, positions, n_seqs, n_heads, n_kv_heads, head_dim, scale, window,
-                    out, lambda n: not (max_len > 0 and n > max_len))
+                    out, lambda n: not (max_len > 0 and n > max_len), sink=sink)
     return out
 
 
 def attention_prefill(q, cache_layer, block_table, cu_seqlens, positions, n_seqs, n_long_tokens, n_heads, n_kv_heads,
-                      head_dim, scale, window, out, min_len=32):
+                      head_dim, scale, window, out, min_len=32, sink=None):
     from pyre_b200.kernels import ops
     assert head_dim in ops.PREFILL_HEAD_DIMS
     taken = _attend_entries(q, cache_layer, block_table, cu_seqlens, positions, n_seqs, n_heads, n_kv_heads, head_dim, scale,
-                            window, out, lambda n: n >= min_len)
+                            window, out, lambda n: n >= min_len, sink=sink)
     assert taken == n_long_tokens, "n_long_tokens must count the tokens of the entries this kernel takes"
     return out
 
 
 def attention_prefill_tc(q, cache_layer, block_table, cu_seqlens, positions, n_seqs, n_long_tokens, n_heads, n_kv_heads,
-                         head_dim, scale, window, out, min_len, key_splits=1):
+                         head_dim, scale, window, out, min_len, key_splits=1, sink=None):
     page_size = cache_layer.shape[3]
     assert 1 <= key_splits <= 32
     assert page_size & (page_size - 1) == 0 and page_size >= 4, "the tcgen05 attention takes power-of-two pages"
     return attention_prefill(q, cache_layer, block_table, cu_seqlens, positions, n_seqs, n_long_tokens, n_heads, n_kv_heads,
-                             head_dim, scale, window, out, min_len)
+                             head_dim, scale, window, out, min_len, sink=sink)
 
 
 def install_bf16(monkeypatch, calls: "dict | None" = None) -> None:
