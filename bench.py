@@ -535,6 +535,120 @@ def run_workload(args) -> dict:
             "ms_first_last": [round(times[1], 2), round(times[-1], 2)]}
 
 
+def run_modovik(args) -> dict:
+    """``--workload modovik``: the Modovik design at layer sizes of the 7B shape (random weights) beside the Qwen2.5
+    decoder at equal sizes and as many layers: a 2,048-token prompt step and decode steps at batch 8 and 64 with
+    2,048 tokens of context, device-timed, and per kernel class the device time of one such step with the
+    fraction of the measured peak (copy bandwidth, or the cuBLAS figure where the flops bind).  Four layers:
+    attention, lightning, attention, an attention layer that reads the third layer's cache."""
+    import numpy as np
+    import torch
+
+    from pyre_b200 import Engine
+    from pyre_b200.config import config_from_dict
+    from pyre_b200.engine.step import StepEntry
+    from pyre_b200.kernels import ops
+
+    peaks = load_peaks()
+    H, I, nh, nkv, hd, V = 3584, 18944, 28, 4, 128, 32768
+    rot = {"dims": 64, "base": 1e6}
+    att = lambda **kw: {"type": "attention", "mixer": dict(heads=nh, kv_heads=nkv, dim=hd, vdim=hd, scale=hd ** -0.5, rot=rot, **kw),
+                        "mlp": {"kind": "dense", "ff": I}}
+    raw_m = {"architecture": "Modovik", "vocab": V, "width": H, "norm": {"eps": 1e-6}, "layers": [
+        att(), {"type": "lightning", "mixer": {"heads": nh, "dim": hd, "vdim": hd, "decay": [1.0 - 2.0 ** (-5 - 3 * i / nh) for i in range(nh)]},
+                "mlp": {"kind": "dense", "ff": I}}, att(), att(kv_from=2)]}
+    L = len(raw_m["layers"])
+    raw_q = dict(CONFIG_7B, num_hidden_layers=L, vocab_size=V)
+    T, ctx_len, reps = PROMPT_LEN, 2048, max(3, args.prefill_reps)
+    rng = np.random.default_rng(0)
+    q, kv = nh * hd, nkv * hd
+
+    def work_modovik(Tn, B, before):
+        """bytes and flops per class of one step of the four layers (three attention layers, one of them without
+        keys and values of its own; one lightning layer)"""
+        keys = B * ((Tn // B) * before + (Tn // B) * (Tn // B + 1) / 2)
+        cached = B * (before + Tn // B)
+        proj_att = 2 * (2 * q + 2 * kv) + (2 * q)          # columns of the stacked projections: q k v g, q k v g, q g
+        proj_lin = 4 * q
+        return {
+            "qkv": {"bytes": (proj_att + proj_lin) * H * 2 + Tn * (L * H + proj_att + proj_lin) * 2, "flops": 2.0 * Tn * H * (proj_att + proj_lin)},
+            "attention": {"bytes": 3 * (cached * 2 * kv * 2 + 2 * Tn * q * 2), "flops": 4.0 * 3 * nh * hd * keys},
+            "linear_attention": {"bytes": Tn * 3 * q * 2 + Tn * q * 4 + B * 2 * nh * hd * hd * 4, "flops": 4.0 * Tn * nh * hd * hd},
+            "o": {"bytes": L * (H * q * 2 + Tn * (q + H) * 2), "flops": 2.0 * L * Tn * q * H},
+            "up": {"bytes": L * (I * H * 2 + Tn * (H + I) * 2), "flops": 2.0 * L * Tn * H * I},
+            "down": {"bytes": L * (H * I * 2 + Tn * (I + H) * 2), "flops": 2.0 * L * Tn * H * I},
+            "activation": {"bytes": L * Tn * I * 4, "flops": 0},
+            "norm": {"bytes": Tn * H * (2 + 4 + 4 + 2), "flops": 0, "per_launch": True},
+            "gate": {"bytes": Tn * q * (2 + 2 + 2), "flops": 0, "per_launch": True},
+            "rotary+write": {"bytes": Tn * (q + 2 * kv) * 2 * 2, "flops": 0, "per_launch": True},
+            "head": {"bytes": V * H * 2 + B * (H * 2 + V * 4), "flops": 2.0 * B * H * V},
+            "embed": {"bytes": Tn * H * (2 + 4), "flops": 0},
+        }
+
+    out = {"workload": "modovik", "layers": L, "peaks": peaks, "sizes": {"width": H, "ff": I, "heads": nh, "kv_heads": nkv,
+           "dim": hd, "vdim": hd, "vocab": V, "prompt": T, "decode_context": ctx_len}, "models": {}}
+    for name, raw in (("modovik", raw_m), ("qwen2", raw_q)):
+        cfg = config_from_dict(raw)
+        biggest = 64
+        eng = Engine(config=cfg, seed=0, dtype="bfloat16", device="cuda:0", page_size=PAGE_SIZE,
+                     max_cache_tokens=biggest * (ctx_len + 256) + 4 * T, max_num_seqs=biggest + 1, max_num_batched_tokens=T,
+                     prefill_chunk=T, max_model_len=ctx_len + 256)
+        st, cache = eng.stepper, eng.cache
+
+        def ev():
+            return torch.cuda.Event(enable_timing=True)
+
+        def prompt(rid, n=T):
+            cache.begin(rid)
+            return st.step([StepEntry(rid, rng.integers(0, V, n).tolist(), [n - 1])])
+
+        for i in range(2):
+            prompt(("warm", i))
+            cache.end(("warm", i))
+        times = []
+        for i in range(reps):
+            a, b = ev(), ev()
+            a.record()
+            prompt(("pf", i))
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b))
+            cache.end(("pf", i))
+        res = {"prefill_ms": round(sorted(times)[len(times) // 2], 3)}
+        res["prefill_tok_s"] = round(T / res["prefill_ms"] * 1e3, 1)
+        with st.kernel_timing() as timer:
+            prompt("timed")
+        cache.end("timed")
+        work = work_modovik(T, 1, 0) if name == "modovik" else class_work(raw_q, L, T, 1, 0, 1)
+        res["prefill_kernels"] = kernel_table(timer.totals(), work, res["prefill_ms"] * 1e3, peaks)
+        for i in range(biggest):
+            prompt(("d", i), ctx_len)
+        for B in (8, 64):
+            reqs = [("d", i) for i in range(B)]
+            step = lambda: st.step([StepEntry(r, [int(rng.integers(0, V))], [0]) for r in reqs])
+            for _ in range(max(4, args.warmup)):
+                step()
+            torch.cuda.synchronize()
+            n = min(args.steps, 32)
+            a, b = ev(), ev()
+            a.record()
+            for _ in range(n):
+                step()
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / n
+            res[f"decode_b{B}_ms"] = round(ms, 4)
+            res[f"decode_b{B}_tok_s"] = round(B / ms * 1e3, 1)
+            with st.kernel_timing() as timer:
+                step()
+            work = work_modovik(B, B, ctx_len + 40) if name == "modovik" else class_work(raw_q, L, B, B, ctx_len + 40, B)
+            res[f"decode_b{B}_kernels"] = kernel_table(timer.totals(), work, ms * 1e3, peaks)
+        out["models"][name] = res
+        del eng, st, cache
+        torch.cuda.empty_cache()
+    return out
+
+
 def run_sweep(args) -> dict:
     """Decode throughput over a grid of batch sizes and context lengths and prefill throughput over
     several portion lengths on the 7B shape, each with its fraction of the roofline (device-timed,
@@ -658,9 +772,10 @@ def main() -> int:
                     help="leave out the points at longer contexts and at the 14B and 32B shapes")
     ap.add_argument("--no-per-kernel", action="store_true",
                     help="leave out the `kernels` block (device time, bytes or flops and fraction of the peak per kernel class)")
-    ap.add_argument("--workload", choices=["serve14b", "mixed32b", "sweep"], default=None,
-                    help="run one of the two other baseline workloads, or a sweep over batch sizes, context lengths and "
-                         "portion lengths on the 7B shape, instead (prints its own JSON line)")
+    ap.add_argument("--workload", choices=["serve14b", "mixed32b", "sweep", "modovik"], default=None,
+                    help="run one of the two other baseline workloads, a sweep over batch sizes, context lengths and "
+                         "portion lengths on the 7B shape, or the Modovik design beside the Qwen2.5 decoder at equal "
+                         "layer sizes, instead (prints its own JSON line)")
     ap.add_argument("--cache-fraction", type=float, default=1.0,
                     help="serve14b: cache capacity as a fraction of what all requests need at once (< 1 forces preemption)")
     args = ap.parse_args()
@@ -668,7 +783,7 @@ def main() -> int:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported, run with --gpus 1")
         return 2
     if args.workload:
-        result = run_sweep(args) if args.workload == "sweep" else run_workload(args)
+        result = run_sweep(args) if args.workload == "sweep" else run_modovik(args) if args.workload == "modovik" else run_workload(args)
         result["env"] = environment()
         print(json.dumps(result))
         return 0

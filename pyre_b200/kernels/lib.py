@@ -49,7 +49,8 @@ SIGNATURES: dict[str, tuple[str, list]] = {
     "pyre_qk_norm_rope_write": ("blockops", [P, LL, I, I, I, P, P, F, P, P, P, P, P, I, I, I, I, I, I, I, I, I, LL, P, P]),
     "pyre_sigmoid_gate": ("blockops", [P, I, P, LL, I, P, I, I, I, I, P]),
     "pyre_rmsnorm_gate": ("blockops", [P, P, P, LL, I, P, I, I, F, I, P]),
-    "pyre_linear_attention_scan": ("linear_attention", [P, LL, I, I, I, P, P, P, P, P, I, I, I, I, I, I, I, P]),
+    "pyre_linear_attention_scan": ("linear_attention", [P, LL, I, I, I, P, P, P, P, P, I, I, I, I, I, I, I, I, P]),
+    "pyre_linear_attention_chunked": ("linear_attention", [P, LL, I, I, I, P, P, P, P, P, I, I, I, I, I, I, I, P]),
 }
 
 _ERRORS = {100001: "bad argument", 100002: "unsupported size"}
@@ -71,6 +72,7 @@ DEFAULT_CLASS = {
     "pyre_attention_prefill_tc": "attention", "pyre_attention_prefill": "attention",
     "pyre_cast_rows": "norm", "pyre_norm_add": "norm", "pyre_activation": "activation", "pyre_qk_norm_rope_write": "rotary+write",
     "pyre_sigmoid_gate": "gate", "pyre_rmsnorm_gate": "gate", "pyre_linear_attention_scan": "linear_attention",
+    "pyre_linear_attention_chunked": "linear_attention",
 }
 
 

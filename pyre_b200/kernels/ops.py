@@ -1203,11 +1203,16 @@ def rmsnorm_gate(o: torch.Tensor, weight: torch.Tensor, eps: float, proj: "torch
 
 def linear_attention(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, state_layer: torch.Tensor,
                      slots: torch.Tensor, cu_seqlens: torch.Tensor, decay: torch.Tensor, n_heads: int, qk_dim: int,
-                     v_dim: int, activation: "str | None" = "silu") -> torch.Tensor:
+                     v_dim: int, activation: "str | None" = "silu", lens=None) -> torch.Tensor:
     """Linear attention with a constant decay per head over the step's entries, continuing each request's state:
     S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t, with q, k, v = act(columns of ``proj``).
     ``state_layer`` [slots, n_heads, qk_dim, v_dim] fp32 is read and left updated at ``slots[b]`` for entry b.
-    Returns fp32 [T, n_heads * v_dim]."""
+    Returns fp32 [T, n_heads * v_dim].
+
+    ``lens``: the entries' token counts on the host.  With them, bfloat16 entries of ``LINEAR_CHUNK_MIN_LEN`` tokens
+    or more run on the tensor cores in chunks of 64 tokens (query/key sizes 64 and 128, value sizes that are
+    multiples of 32, 16-byte aligned columns); everything else, and all of float32, walks token by token in fp32,
+    bit-identical under any cutting."""
     _check(proj, "proj", dim=2)
     _check(state_layer, "state_layer", torch.float32, 4)
     _check(slots, "slots", torch.int32, 1)
@@ -1224,10 +1229,29 @@ def linear_attention(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, sta
     if activation not in (None, "silu"):
         raise UnsupportedSize(f"linear attention: activation {activation!r} is not implemented")
     out = torch.empty((T, n_heads * v_dim), dtype=torch.float32, device=proj.device)
+    act = 1 if activation == "silu" else 0
+    max_len = 0
+    if lens is not None and USE_LINEAR_CHUNKS and proj.dtype == torch.bfloat16 and linear_chunks_ok(W, q_col, k_col, v_col, qk_dim, v_dim) \
+            and int(max(lens)) >= LINEAR_CHUNK_MIN_LEN:
+        lib.call("pyre_linear_attention_chunked", proj.data_ptr(), W, int(q_col), int(k_col), int(v_col), state_layer.data_ptr(),
+                 slots.data_ptr(), cu_seqlens.data_ptr(), decay.data_ptr(), out.data_ptr(), T, n_seqs, n_heads, qk_dim, v_dim,
+                 act, LINEAR_CHUNK_MIN_LEN, _stream())
+        if int(min(lens)) >= LINEAR_CHUNK_MIN_LEN:
+            return out
+        max_len = LINEAR_CHUNK_MIN_LEN - 1
     lib.call("pyre_linear_attention_scan", proj.data_ptr(), W, int(q_col), int(k_col), int(v_col), state_layer.data_ptr(),
              slots.data_ptr(), cu_seqlens.data_ptr(), decay.data_ptr(), out.data_ptr(), T, n_seqs, n_heads, qk_dim, v_dim,
-             1 if activation == "silu" else 0, _dt(proj.dtype), _stream())
+             act, _dt(proj.dtype), max_len, _stream())
     return out
+
+
+USE_LINEAR_CHUNKS = True
+LINEAR_CHUNK_MIN_LEN = 32     # entries with at least this many tokens go to the tensor-core kernel
+
+
+def linear_chunks_ok(row_width: int, q_col: int, k_col: int, v_col: int, qk_dim: int, v_dim: int) -> bool:
+    """The sizes the tensor-core linear attention takes (as its launcher checks them)."""
+    return qk_dim in (64, 128) and v_dim % 32 == 0 and row_width % 8 == 0 and q_col % 8 == 0 and k_col % 8 == 0 and v_col % 8 == 0
 
 
 def attention_row_dim(qk_dim: int, v_dim: int, dtype: torch.dtype) -> int:

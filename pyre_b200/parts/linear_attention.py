@@ -77,7 +77,8 @@ class DecayLinearAttention(Part):
         with lib.section("qkv"):
             proj = ops.materialize(ops.linear(h, self.w_proj))
         o = ops.linear_attention(proj, self.q_col, self.k_col, self.v_col, st.buffer[call.state_layer], st.slots,
-                                 ctx.cu_seqlens, self.decay, self.n_heads, self.head_dim, self.v_head_dim, self.activation)
+                                 ctx.cu_seqlens, self.decay, self.n_heads, self.head_dim, self.v_head_dim, self.activation,
+                                 lens=ctx.cu_seqlens_host[1:] - ctx.cu_seqlens_host[:-1])
         a = ops.rmsnorm_gate(o, self.norm_w, self.eps, proj if self.out_gate else None, self.g_col, self.dtype)
         with lib.section("o"):
             return ops.linear(a, self.w_o, partials_ok=True)

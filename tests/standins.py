@@ -150,7 +150,7 @@ def rmsnorm_gate(o, weight, eps, proj, g_col, out_dtype):
 
 
 def linear_attention(proj, q_col, k_col, v_col, state_layer, slots, cu_seqlens, decay, n_heads, qk_dim, v_dim,
-                     activation="silu"):
+                     activation="silu", lens=None):
     T = proj.shape[0]
     x = proj.float()
     act = torch.nn.functional.silu if activation == "silu" else (lambda z: z)

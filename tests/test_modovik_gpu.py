@@ -243,8 +243,9 @@ def test_linear_attention_over_state_slots(ops, dtype, Hn, dk, dv, decay):
     for s in seqs:
         x = s.double().cpu()
         n = x.shape[0]
-        qq, kk = MP.silu(x[:, q_col:q_col + Hn * dk]).reshape(n, Hn, dk), MP.silu(x[:, k_col:k_col + Hn * dk]).reshape(n, Hn, dk)
-        vv = MP.silu(x[:, v_col:v_col + Hn * dv]).reshape(n, Hn, dv)
+        rb = (lambda z: z.to(torch.bfloat16).double()) if dtype == torch.bfloat16 else (lambda z: z)      # q, k, v are activations
+        qq, kk = rb(MP.silu(x[:, q_col:q_col + Hn * dk])).reshape(n, Hn, dk), rb(MP.silu(x[:, k_col:k_col + Hn * dk])).reshape(n, Hn, dk)
+        vv = rb(MP.silu(x[:, v_col:v_col + Hn * dv])).reshape(n, Hn, dv)
         want.append(MP.decayed_linear_attention(qq, kk, vv, d.double().cpu()).reshape(n, Hn * dv))
     state = torch.full((6, Hn, dk, dv), float("nan"), device="cuda")
     slot_of = [4, 0, 5, 2]
@@ -266,6 +267,59 @@ def test_linear_attention_over_state_slots(ops, dtype, Hn, dk, dv, decay):
         g_b, w_b = torch.cat(got[b]).double().cpu(), want[b]
         scale = float(w_b.abs().max())
         assert (g_b - w_b).abs().max() <= 2e-5 * scale + 1e-6, f"entry {b}: {(g_b - w_b).abs().max():.3e} of {scale:.3e}"
+
+
+@pytest.mark.parametrize("Hn,dk,dv,decay", [(3, 64, 32, [0.5, 0.97, 1.0]), (2, 128, 64, [0.999, 0.9]), (1, 128, 128, [0.99]),
+                                            (4, 64, 96, [0.3, 0.8, 0.995, 0.9999])])
+def test_linear_attention_on_the_tensor_cores(ops, Hn, dk, dv, decay):
+    """Prompt portions of 32 tokens and more take the chunked kernel (chunks of 64 tokens; a portion of exactly one
+    chunk, one token more, a ragged end), shorter entries beside them the token-by-token kernel, and a request goes
+    from one to the other and back between steps with its state; the result is that of the recurrence on the same
+    bf16-rounded q, k, v up to the rounding of sums.  A far key decides an output 287 tokens on."""
+    g = torch.Generator(device="cuda").manual_seed(dk + dv)
+    lens = [300, 37, 64, 65, 2, 131]
+    W = 8 + Hn * (2 * dk + dv)
+    q_col, k_col, v_col = 8, 8 + Hn * dk, 8 + 2 * Hn * dk
+    assert ops.linear_chunks_ok(W, q_col, k_col, v_col, dk, dv)
+    seqs = [torch.randn(n, W, device="cuda", generator=g) * (1.0 if dk <= 64 else 0.6) for n in lens]
+    seqs[0][3, k_col:k_col + dk] = 6.0
+    seqs[0][290, q_col:q_col + dk] = 6.0
+    seqs = [s.to(torch.bfloat16) for s in seqs]
+    d = torch.tensor(decay, dtype=torch.float32, device="cuda")
+    rb = lambda x: x.to(torch.bfloat16).double()
+    want = []
+    for s in seqs:
+        x = s.double().cpu()
+        n = x.shape[0]
+        qq, kk = rb(MP.silu(x[:, q_col:q_col + Hn * dk])).reshape(n, Hn, dk), rb(MP.silu(x[:, k_col:k_col + Hn * dk])).reshape(n, Hn, dk)
+        vv = rb(MP.silu(x[:, v_col:v_col + Hn * dv])).reshape(n, Hn, dv)
+        want.append(MP.decayed_linear_attention(qq, kk, vv, d.double().cpu()).reshape(n, Hn * dv))
+    state = torch.full((8, Hn, dk, dv), float("nan"), device="cuda")
+    slot_of = [4, 0, 5, 2, 7, 1]
+    state[slot_of] = 0.0
+    got = [[] for _ in lens]
+    # entry 0: 170 tokens (chunks), then 31 (token by token), then 99 (chunks); entry 5: 1 token, then 130 (chunks)
+    cuts = [[0, 170, 201, 300], [0, 37, 37, 37], [0, 0, 64, 64], [0, 65, 65, 65], [0, 0, 2, 2], [0, 1, 131, 131]]
+    for step in range(3):
+        rows, slots, cu, who = [], [], [0], []
+        for b, s in enumerate(seqs):
+            lo, hi = cuts[b][step], cuts[b][step + 1]
+            if hi > lo:
+                rows.append(s[lo:hi]); slots.append(slot_of[b]); cu.append(cu[-1] + hi - lo); who.append(b)
+        out = ops.linear_attention(torch.cat(rows).contiguous(), q_col, k_col, v_col, state, torch.tensor(slots, dtype=torch.int32, device="cuda"),
+                                   torch.tensor(cu, dtype=torch.int32, device="cuda"), d, Hn, dk, dv, "silu", lens=np.diff(np.asarray(cu)))
+        for i, b in enumerate(who):
+            got[b].append(out[cu[i]:cu[i + 1]])
+    assert torch.isnan(state[[3, 6]]).all(), "slots of no entry were touched"
+    assert torch.isfinite(state[slot_of]).all()
+    for b in range(len(lens)):
+        g_b, w_b = torch.cat(got[b]).double().cpu(), want[b]
+        assert torch.isfinite(g_b).all(), f"entry {b}"
+        err = (g_b - w_b).abs().max(dim=1).values
+        scale = w_b.abs().max(dim=1).values.clamp_min(float(w_b.abs().mean()))
+        bad = err > 3e-4 * scale + 1e-5
+        assert not bad.any(), f"entry {b}: first wrong token {int(torch.where(bad)[0][0])} of {lens[b]}: {float(err[bad][0]):.3e} of {float(scale[bad][0]):.3e}"
+    ops.check_device_errors()
 
 
 # --------------------------------------------------------------------------- the engine against the plain model
