@@ -123,7 +123,8 @@ PYRE_API int pyre_linear_attention_scan(const void* proj, long long row_stride, 
 }
 
 // ---------------------------------------------------------------------------
-// The same recurrence for prompt portions, on the tensor cores, in chunks of 64 tokens (bfloat16 activations).
+// The same recurrence for prompt portions, on the tensor cores, in chunks of 64 tokens (query/key size 64) or 128
+// tokens (query/key size 128) (bfloat16 activations).
 // For the tokens i, j of a chunk that starts from the state S (n tokens, w = decay):
 //   A[i][j] = (q_i . k_j) w^(i-j)  for j <= i, else 0                       (fp32 scores, decays applied in fp32)
 //   o_i     = sum_j A[i][j] v_j  +  w^(i+1) S^T q_i
@@ -133,15 +134,14 @@ PYRE_API int pyre_linear_attention_scan(const void* proj, long long row_stride, 
 // and the remainder rounded: 16 bits of mantissa), so they are not rounded to 8 bits on the way.  q, k and v
 // are silu(projection) rounded to bf16 once.
 //
-// Grid (tiles of 32 value columns, heads, entries); four warps.  Warp w owns the chunk's tokens 16 w .. 16 w + 15
-// for the outputs, and rows [w DK / 4, (w + 1) DK / 4) of the state tile [DK, 32], which it keeps in MMA accumulator
+// Grid (tiles of 32 value columns, heads, entries); four or eight warps.  Warp w owns the chunk's tokens 16 w .. 16 w + 15
+// for the outputs, and 16 rows of the state tile [DK, 32], which it keeps in MMA accumulator
 // registers; the state's two bf16 halves are left in shared memory for the other warps' q S products.  The next
 // chunk's q, k, v rows arrive by cp.async while a chunk is computed.  Entries shorter than min_len are left to
 // the scan kernel.  The result differs from the scan's by rounding only.
 // ---------------------------------------------------------------------------
 namespace {
 
-constexpr int LC_CHUNK = 64;
 constexpr int LC_COLS = 32;
 constexpr int LC_VP = LC_COLS + 8;      // pitch of the value and state tiles in shared memory (elements)
 
@@ -171,20 +171,26 @@ __device__ __forceinline__ void lc_cp16(uint32_t dst, const void* src, bool real
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(n) : "memory");
 }
 
-template <int DK>
-__global__ void __launch_bounds__(128)
+// silu for operands that are rounded to bfloat16 at once: the fast exponential and division are exact enough
+__device__ __forceinline__ float lc_silu(float z) { return __fdividef(z, 1.0f + __expf(-z)); }
+
+// WARPS warps; a chunk is 16 WARPS tokens (64 or 128)
+template <int DK, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32)
 linear_attention_chunk_kernel(const __nv_bfloat16* proj, long long row_stride, int q_col, int k_col, int v_col, float* state,
                               const int* slots, const int* cu_seqlens, const float* decay, float* out, int H, int dv,
                               int act, int min_len) {
     constexpr int QP = DK + 8;            // pitch of the q and k tiles (elements): rows 16 bytes apart in banks
-    constexpr int MT = DK / 64;           // 16-row tiles of the state per warp
+    constexpr int LC_CHUNK = 16 * WARPS, NTH = 32 * WARPS;
+    constexpr int MT = DK / LC_CHUNK;     // 16-row tiles of the state per warp
+    static_assert(MT >= 1 && MT * LC_CHUNK == DK, "every warp owns whole 16-row tiles of the state");
     extern __shared__ __align__(16) unsigned char lc_smem[];
     __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(lc_smem);                 // [2][64][QP]
     __nv_bfloat16* sK = sQ + 2 * LC_CHUNK * QP;                                    // [2][64][QP]
     __nv_bfloat16* sV = sK + 2 * LC_CHUNK * QP;                                    // [2][64][LC_VP]
     __nv_bfloat16* sSh = sV + 2 * LC_CHUNK * LC_VP;                                // [DK][LC_VP] state, rounded
     __nv_bfloat16* sSl = sSh + DK * LC_VP;                                         // [DK][LC_VP] state, remainder
-    float* pw = reinterpret_cast<float*>(sSl + DK * LC_VP);                        // [65] powers of the decay
+    float* pw = reinterpret_cast<float*>(sSl + DK * LC_VP);                        // [chunk + 1] powers of the decay
     pdl_trigger();
     pdl_wait();
     const int h = blockIdx.y, seq = blockIdx.z, col0 = blockIdx.x * LC_COLS;
@@ -202,13 +208,13 @@ linear_attention_chunk_kernel(const __nv_bfloat16* proj, long long row_stride, i
         __nv_bfloat16* q = sQ + stage * LC_CHUNK * QP;
         __nv_bfloat16* k = sK + stage * LC_CHUNK * QP;
         __nv_bfloat16* v = sV + stage * LC_CHUNK * LC_VP;
-        for (int e = threadIdx.x; e < LC_CHUNK * (DK / 8); e += 128) {
+        for (int e = threadIdx.x; e < LC_CHUNK * (DK / 8); e += NTH) {
             const int r = e / (DK / 8), c = (e - r * (DK / 8)) * 8;
             const size_t row = (size_t)(c0 + (r < n ? r : 0)) * row_stride;
             lc_cp16((uint32_t)__cvta_generic_to_shared(q + r * QP + c), q_src + row + c, r < n);
             lc_cp16((uint32_t)__cvta_generic_to_shared(k + r * QP + c), k_src + row + c, r < n);
         }
-        for (int e = threadIdx.x; e < LC_CHUNK * (LC_COLS / 8); e += 128) {
+        for (int e = threadIdx.x; e < LC_CHUNK * (LC_COLS / 8); e += NTH) {
             const int r = e / (LC_COLS / 8), c = (e - r * (LC_COLS / 8)) * 8;
             const size_t row = (size_t)(c0 + (r < n ? r : 0)) * row_stride;
             lc_cp16((uint32_t)__cvta_generic_to_shared(v + r * LC_VP + c), v_src + row + c, r < n);
@@ -222,7 +228,7 @@ linear_attention_chunk_kernel(const __nv_bfloat16* proj, long long row_stride, i
         for (int i = 0; i <= LC_CHUNK; ++i) { pw[i] = p; p *= lam; }
     }
     // this warp's rows of the state tile, as accumulator fragments: element (row m0 + 16 mt + g (+ 8), column 8 nt + 2 t (+ 1))
-    const int m0 = warp * (DK / 4);
+    const int m0 = warp * (DK / WARPS);
     float S[MT][4][4];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
@@ -257,19 +263,19 @@ linear_attention_chunk_kernel(const __nv_bfloat16* proj, long long row_stride, i
         __nv_bfloat16* k = sK + stage * LC_CHUNK * QP;
         __nv_bfloat16* v = sV + stage * LC_CHUNK * LC_VP;
         if (act == 1) {
-            for (int e = threadIdx.x; e < LC_CHUNK * (DK / 2); e += 128) {
+            for (int e = threadIdx.x; e < LC_CHUNK * (DK / 2); e += NTH) {
                 const int r = e / (DK / 2), c = (e - r * (DK / 2)) * 2;
                 __nv_bfloat162* pq = reinterpret_cast<__nv_bfloat162*>(q + r * QP + c);
                 __nv_bfloat162* pk = reinterpret_cast<__nv_bfloat162*>(k + r * QP + c);
                 const float2 a = __bfloat1622float2(*pq), b = __bfloat1622float2(*pk);
-                *pq = __floats2bfloat162_rn(la_act(a.x, 1), la_act(a.y, 1));
-                *pk = __floats2bfloat162_rn(la_act(b.x, 1), la_act(b.y, 1));
+                *pq = __floats2bfloat162_rn(lc_silu(a.x), lc_silu(a.y));
+                *pk = __floats2bfloat162_rn(lc_silu(b.x), lc_silu(b.y));
             }
-            for (int e = threadIdx.x; e < LC_CHUNK * (LC_COLS / 2); e += 128) {
+            for (int e = threadIdx.x; e < LC_CHUNK * (LC_COLS / 2); e += NTH) {
                 const int r = e / (LC_COLS / 2), c = (e - r * (LC_COLS / 2)) * 2;
                 __nv_bfloat162* pv = reinterpret_cast<__nv_bfloat162*>(v + r * LC_VP + c);
                 const float2 a = __bfloat1622float2(*pv);
-                *pv = __floats2bfloat162_rn(la_act(a.x, 1), la_act(a.y, 1));
+                *pv = __floats2bfloat162_rn(lc_silu(a.x), lc_silu(a.y));
             }
             __syncthreads();
         }
@@ -278,10 +284,12 @@ linear_attention_chunk_kernel(const __nv_bfloat16* proj, long long row_stride, i
         const uint32_t sh_s = (uint32_t)__cvta_generic_to_shared(sSh), sl_s = (uint32_t)__cvta_generic_to_shared(sSl);
         const int i0 = 16 * warp;      // this warp's tokens of the chunk
 
-        // ---- scores of this warp's 16 tokens against the chunk's 64 keys, and q S for the same tokens
-        float sc[8][4], oi[4][4];
+        // ---- scores of this warp's 16 tokens against the chunk's keys up to its own (later keys are masked anyway),
+        // and q S for the same tokens; a warp whose tokens lie beyond the portion's end has nothing to do here
+        if (i0 < n) {
+        float sc[2 * WARPS][4], oi[4][4];
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt) { sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f; }
+        for (int nt = 0; nt < 2 * WARPS; ++nt) { sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f; }
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt) { oi[nt][0] = oi[nt][1] = oi[nt][2] = oi[nt][3] = 0.f; }
 #pragma unroll
@@ -289,7 +297,8 @@ linear_attention_chunk_kernel(const __nv_bfloat16* proj, long long row_stride, i
             uint32_t a[4];
             lc_ldsm(a, q_s + (uint32_t)(((i0 + (lane & 7) + ((lane >> 3) & 1) * 8) * QP + 16 * ks + (lane >> 4) * 8) * 2));
 #pragma unroll
-            for (int np = 0; np < 4; ++np) {       // keys 16 np .. 16 np + 15
+            for (int np = 0; np < WARPS; ++np) {       // keys 16 np .. 16 np + 15
+                if (np > warp) continue;
                 uint32_t b[4];
                 lc_ldsm(b, k_s + (uint32_t)(((16 * np + (lane & 7) + (lane >> 4) * 8) * QP + 16 * ks + ((lane >> 3) & 1) * 8) * 2));
                 lc_mma(sc[2 * np], a, b[0], b[1]);
@@ -314,7 +323,7 @@ linear_attention_chunk_kernel(const __nv_bfloat16* proj, long long row_stride, i
             o[nt][0] = oi[nt][0] * wa; o[nt][1] = oi[nt][1] * wa; o[nt][2] = oi[nt][2] * wb; o[nt][3] = oi[nt][3] * wb;
         }
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
+        for (int nt = 0; nt < 2 * WARPS; ++nt) {
             const int j = 8 * nt + 2 * t;
             sc[nt][0] = j <= ia ? sc[nt][0] * pw[ia - j] : 0.f;
             sc[nt][1] = j + 1 <= ia ? sc[nt][1] * pw[ia - j - 1] : 0.f;
@@ -323,7 +332,8 @@ linear_attention_chunk_kernel(const __nv_bfloat16* proj, long long row_stride, i
         }
         // ---- o += A v  (A as two bf16 halves; keys 16 kk .. 16 kk + 15 per step)
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
+        for (int kk = 0; kk < WARPS; ++kk) {
+            if (kk > warp) continue;
             uint32_t ah[4], al[4];
             lc_split(sc[2 * kk][0], sc[2 * kk][1], ah[0], al[0]);
             lc_split(sc[2 * kk][2], sc[2 * kk][3], ah[1], al[1]);
@@ -343,6 +353,7 @@ linear_attention_chunk_kernel(const __nv_bfloat16* proj, long long row_stride, i
             if (ia < n) *reinterpret_cast<float2*>(dst) = make_float2(o[nt][0], o[nt][1]);
             if (ib < n) *reinterpret_cast<float2*>(dst + (size_t)8 * H * dv) = make_float2(o[nt][2], o[nt][3]);
         }
+        }
         __syncthreads();      // every warp has read the old state's halves
         // ---- the state after the chunk: S = w^n S + K^T (w^(n - 1 - j) v_j)
         const float wn = pw[n];
@@ -353,7 +364,8 @@ linear_attention_chunk_kernel(const __nv_bfloat16* proj, long long row_stride, i
                 S[mt][nt][0] *= wn; S[mt][nt][1] *= wn; S[mt][nt][2] *= wn; S[mt][nt][3] *= wn;
             }
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
+        for (int kk = 0; kk < WARPS; ++kk) {
+            if (16 * kk >= n) continue;
             // the decayed values of tokens 16 kk .., as B fragments in two halves: a lane holds tokens 16 kk + 2 t (+ 1) (+ 8)
             const int j0 = 16 * kk + 2 * t;
             const float w0 = j0 < n ? pw[n - 1 - j0] : 0.f, w1 = j0 + 1 < n ? pw[n - 2 - j0] : 0.f;
@@ -396,18 +408,19 @@ linear_attention_chunk_kernel(const __nv_bfloat16* proj, long long row_stride, i
         }
 }
 
-template <int DK>
+template <int DK, int WARPS>
 int lc_launch(dim3 grid, cudaStream_t stream, const __nv_bfloat16* proj, long long row_stride, int q_col, int k_col, int v_col,
               float* state, const int* slots, const int* cu_seqlens, const float* decay, float* out, int H, int dv, int act, int min_len) {
-    constexpr size_t SMEM = (size_t)(4 * LC_CHUNK * (DK + 8) + 2 * LC_CHUNK * LC_VP + 2 * DK * LC_VP) * 2 + 72 * sizeof(float);
+    constexpr int LC_CHUNK = 16 * WARPS;
+    constexpr size_t SMEM = (size_t)(4 * LC_CHUNK * (DK + 8) + 2 * LC_CHUNK * LC_VP + 2 * DK * LC_VP) * 2 + (LC_CHUNK + 8) * sizeof(float);
     static bool configured_on[PYRE_MAX_DEVICES] = {};
     bool& configured = configured_on[pyre_current_device()];
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(linear_attention_chunk_kernel<DK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
+        cudaError_t e = cudaFuncSetAttribute(linear_attention_chunk_kernel<DK, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    pyre_launch(linear_attention_chunk_kernel<DK>, grid, dim3(128), SMEM, stream, proj, row_stride, q_col, k_col, v_col, state, slots,
+    pyre_launch(linear_attention_chunk_kernel<DK, WARPS>, grid, dim3(WARPS * 32), SMEM, stream, proj, row_stride, q_col, k_col, v_col, state, slots,
                 cu_seqlens, decay, out, H, dv, act, min_len);
     return (int)cudaGetLastError();
 }
@@ -431,6 +444,6 @@ PYRE_API int pyre_linear_attention_chunked(const void* proj, long long row_strid
         return PYRE_ERR_UNSUPPORTED;
     const dim3 grid(dv / LC_COLS, H, n_seqs);
     const __nv_bfloat16* p = (const __nv_bfloat16*)proj;
-    return dk == 64 ? lc_launch<64>(grid, stream, p, row_stride, q_col, k_col, v_col, state, slots, cu_seqlens, decay, out, H, dv, act, min_len)
-                    : lc_launch<128>(grid, stream, p, row_stride, q_col, k_col, v_col, state, slots, cu_seqlens, decay, out, H, dv, act, min_len);
+    return dk == 64 ? lc_launch<64, 4>(grid, stream, p, row_stride, q_col, k_col, v_col, state, slots, cu_seqlens, decay, out, H, dv, act, min_len)
+                    : lc_launch<128, 8>(grid, stream, p, row_stride, q_col, k_col, v_col, state, slots, cu_seqlens, decay, out, H, dv, act, min_len);
 }
