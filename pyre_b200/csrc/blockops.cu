@@ -69,11 +69,83 @@ __global__ void norm_add_kernel(float* x, const T* y, const float* partials, int
     }
 }
 
+// The same for rows of H = 4 m elements: vectors of four, and a thread keeps its (at most KEEP) vectors of the branch
+// output in registers between the sum of squares and the update, so the output is read once.  The sums are those
+// of the scalar kernel in another order; a row's order depends on H alone.
+template <typename T, int KEEP>
+__global__ void norm_add_vec_kernel(float* x, const T* y, const float* partials, int n_partials, long long partial_stride,
+                                    const float* w, T* next, int H, float eps) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const T* yr = y ? y + (size_t)r * H : nullptr;
+    const float* pr = partials ? partials + (size_t)r * H : nullptr;
+    Vec<float, 4> kept[KEEP];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < KEEP; ++j) {
+        const int i = (threadIdx.x + j * blockDim.x) * 4;
+        if (i < H) {
+            Vec<float, 4> v;
+            if (pr) {
+                v = load_vec<float, 4>(pr + i);
+                for (int s = 1; s < n_partials; ++s) {
+                    const Vec<float, 4> q = load_vec<float, 4>(pr + (size_t)s * partial_stride + i);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) v.v[k] += q.v[k];
+                }
+            } else {
+                const Vec<T, 4> a = load_vec<T, 4>(yr + i);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) v.v[k] = to_f32<T>(a.v[k]);
+            }
+            kept[j] = v;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) ss = fmaf(v.v[k], v.v[k], ss);
+        }
+    }
+    const float total = block_sum(ss, scratch);
+    const float rstd = 1.0f / sqrtf(total / (float)H + eps);
+    float* xr = x + (size_t)r * H;
+#pragma unroll
+    for (int j = 0; j < KEEP; ++j) {
+        const int i = (threadIdx.x + j * blockDim.x) * 4;
+        if (i < H) {
+            Vec<float, 4> a = load_vec<float, 4>(xr + i);
+            const Vec<float, 4> g = load_vec<float, 4>(w + i);
+            Vec<T, 4> o;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                a.v[k] = a.v[k] + __fmul_rn(__fmul_rn(kept[j].v[k], rstd), g.v[k]);
+                o.v[k] = from_f32<T>(a.v[k]);
+            }
+            store_vec<float, 4>(xr + i, a);
+            if (next) store_vec<T, 4>(next + (size_t)r * H + i, o);
+        }
+    }
+}
+
 PYRE_API int pyre_norm_add(float* x, const void* y, const float* partials, int n_partials, long long partial_stride,
                            const float* weight, void* next, int n_rows, int H, float eps, int dtype, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if ((y == nullptr) == (partials == nullptr)) return PYRE_ERR_BAD_ARG;
     if (partials && n_partials < 1) return PYRE_ERR_BAD_ARG;
+    if (H % 4 == 0 && H <= 512 * 4 * 4 && partial_stride % 4 == 0 &&
+        (((uintptr_t)x | (uintptr_t)partials | (uintptr_t)weight | (uintptr_t)y | (uintptr_t)next) & 15) == 0) {
+        const int per = H / 4;
+        const int threads = min(512, max(32, ((per + 31) / 32) * 32));
+        const int per_thread = ceil_div(per, threads);
+#define NA(TT, KP) pyre_launch(norm_add_vec_kernel<TT, KP>, dim3(n_rows), dim3(threads), 0, stream, x, (const TT*)y, partials, n_partials, partial_stride, weight, (TT*)next, H, eps)
+#define NA_PICK(TT) do { if (per_thread <= 1) NA(TT, 1); else if (per_thread <= 2) NA(TT, 2); else NA(TT, 4); } while (0)
+        if (dtype == PYRE_BF16) NA_PICK(__nv_bfloat16);
+        else if (dtype == PYRE_F32) NA_PICK(float);
+        else return PYRE_ERR_BAD_ARG;
+#undef NA_PICK
+#undef NA
+        PYRE_LAUNCH_CHECK();
+        return 0;
+    }
     const int threads = min(512, max(32, ((H + 31) / 32) * 32));
     if (dtype == PYRE_BF16)
         pyre_launch(norm_add_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, x, (const __nv_bfloat16*)y, partials, n_partials, partial_stride, weight, (__nv_bfloat16*)next, H, eps);
@@ -106,13 +178,34 @@ __global__ void activation_kernel(const T* in, T* out, size_t n) {
     }
 }
 
+// the same in vectors of 16 bytes (n a multiple of VEC, both pointers aligned)
+template <typename T, int KIND, int VEC>
+__global__ void activation_vec_kernel(const T* in, T* out, size_t n_vec) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
+        Vec<T, VEC> a = load_vec<T, VEC>(in + i * VEC), o;
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+            const float z = to_f32<T>(a.v[k]);
+            o.v[k] = from_f32<T>(KIND == 0 ? act_silu(z) : act_gelu_tanh(z));
+        }
+        store_vec<T, VEC>(out + i * VEC, o);
+    }
+}
+
 PYRE_API int pyre_activation(const void* in, void* out, long long n, int kind, int dtype, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (kind != 0 && kind != 1) return PYRE_ERR_BAD_ARG;
-    const int blocks = (int)min((long long)4096, ceil_div_ll(n, 256));
-#define ACT(TT, K) pyre_launch(activation_kernel<TT, K>, dim3(blocks), dim3(256), 0, stream, (const TT*)in, (TT*)out, (size_t)n)
-    if (dtype == PYRE_BF16) { if (kind == 0) ACT(__nv_bfloat16, 0); else ACT(__nv_bfloat16, 1); }
-    else if (dtype == PYRE_F32) { if (kind == 0) ACT(float, 0); else ACT(float, 1); }
+    const int vec = dtype == PYRE_BF16 ? 8 : 4;
+    const bool vector = n % vec == 0 && (((uintptr_t)in | (uintptr_t)out) & 15) == 0;
+    const long long items = vector ? n / vec : n;
+    const int blocks = (int)min((long long)148 * 16, ceil_div_ll(items, 256));
+#define ACT(TT, K, V) do { if (vector) pyre_launch(activation_vec_kernel<TT, K, V>, dim3(blocks), dim3(256), 0, stream, (const TT*)in, (TT*)out, (size_t)items); \
+                           else pyre_launch(activation_kernel<TT, K>, dim3(blocks), dim3(256), 0, stream, (const TT*)in, (TT*)out, (size_t)n); } while (0)
+    if (dtype == PYRE_BF16) { if (kind == 0) ACT(__nv_bfloat16, 0, 8); else ACT(__nv_bfloat16, 1, 8); }
+    else if (dtype == PYRE_F32) { if (kind == 0) ACT(float, 0, 4); else ACT(float, 1, 4); }
     else return PYRE_ERR_BAD_ARG;
 #undef ACT
     PYRE_LAUNCH_CHECK();
@@ -233,10 +326,47 @@ __global__ void sigmoid_gate_kernel(const T* a, int a_dim, const T* proj, long l
     }
 }
 
+// the same in vectors of VEC elements along a head (dv, a_dim, g_col and row_stride multiples of VEC, aligned pointers)
+template <typename T, int VEC>
+__global__ void sigmoid_gate_vec_kernel(const T* a, int a_dim, const T* proj, long long row_stride, int g_col, T* out,
+                                        int n_tokens, int nh, int dv) {
+    pdl_trigger();
+    pdl_wait();
+    const int per_head = dv / VEC;
+    const size_t n = (size_t)n_tokens * nh * per_head, stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const size_t t = i / ((size_t)nh * per_head);
+        const int c = (int)(i - t * nh * per_head), h = c / per_head, j = (c - h * per_head) * VEC;
+        Vec<T, VEC> v = load_vec<T, VEC>(a + (t * nh + h) * a_dim + j), o;
+        if (g_col >= 0) {
+            const Vec<T, VEC> gt = load_vec<T, VEC>(proj + t * row_stride + g_col + h * dv + j);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) o.v[k] = from_f32<T>(to_f32<T>(v.v[k]) * act_sigmoid(to_f32<T>(gt.v[k])));
+        } else {
+            o = v;
+        }
+        store_vec<T, VEC>(out + (t * nh + h) * dv + j, o);
+    }
+}
+
 PYRE_API int pyre_sigmoid_gate(const void* a, int a_dim, const void* proj, long long row_stride, int g_col, void* out,
                                int n_tokens, int nh, int dv, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (a_dim < dv || dv <= 0 || nh <= 0 || (g_col >= 0 && !proj)) return PYRE_ERR_BAD_ARG;
+    {
+        const int vec = dtype == PYRE_BF16 ? 8 : 4;
+        if (dv % vec == 0 && a_dim % vec == 0 && (g_col < 0 || (g_col % vec == 0 && row_stride % vec == 0)) &&
+            (((uintptr_t)a | (uintptr_t)out | (uintptr_t)proj) & 15) == 0 && (dtype == PYRE_BF16 || dtype == PYRE_F32)) {
+            const long long items = (long long)n_tokens * nh * (dv / vec);
+            const int blocks = (int)min((long long)148 * 16, ceil_div_ll(items, 256));
+            if (dtype == PYRE_BF16)
+                pyre_launch(sigmoid_gate_vec_kernel<__nv_bfloat16, 8>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)a, a_dim, (const __nv_bfloat16*)proj, row_stride, g_col, (__nv_bfloat16*)out, n_tokens, nh, dv);
+            else
+                pyre_launch(sigmoid_gate_vec_kernel<float, 4>, dim3(blocks), dim3(256), 0, stream, (const float*)a, a_dim, (const float*)proj, row_stride, g_col, (float*)out, n_tokens, nh, dv);
+            PYRE_LAUNCH_CHECK();
+            return 0;
+        }
+    }
     const long long n = (long long)n_tokens * nh * dv;
     const int blocks = (int)min((long long)4096, ceil_div_ll(n, 256));
     if (dtype == PYRE_BF16)
