@@ -176,6 +176,8 @@ struct GemmParams {
     int x_is_constant;            // 1: X holds weights (may be loaded before the kernels before this one finish); 0: Y does
     int gated;                    // 1: the weight rows are gate/up rows interleaved in blocks of 64 (gate rows, then the up
                                   // rows of the same features); the epilogue writes silu(gate) * up, half as many features
+    int act;                      // 1 (row store, one split, bf16 out, FOLD == 1 variants): out = gelu_tanh(product), applied to the
+                                  // product rounded to bfloat16, as an activation kernel of its own would read it
     int* err_flag;
     // ---- work folded into the product so that no small kernel runs around it.  With the transposed store (few
     // tokens, the weights on the MMA's rows) as described below; with the row store (many tokens in one split, an
@@ -239,6 +241,15 @@ struct SmemLayout {
 // drains its own 128 accumulator rows.  Barriers: the first CTA's "full" barriers count the bytes of both CTAs'
 // loads; the MMA commits arrive on the "empty" and "accumulator full" barriers of both; the epilogue warps of
 // both arrive on the first CTA's "accumulator empty" barriers.
+// the tanh form of gelu on a product that is rounded to bfloat16 first: 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))
+__device__ __forceinline__ float gelu_tanh_of_bf16(float acc) {
+    const float z = __bfloat162float(__float2bfloat16_rn(acc));
+    // the result is rounded to bfloat16 (2^-9): the hardware tanh (2^-11) is exact enough, and the epilogue has no time for more
+    float th;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    return 0.5f * z * (1.0f + th);
+}
+
 template <int BN, int STAGES, bool X_CONTIGUOUS_OUT, int CTAS = 1, int FOLD = 1>
 __global__ void __launch_bounds__(THREADS, (X_CONTIGUOUS_OUT && FOLD != 0) ? 5 : (!X_CONTIGUOUS_OUT && FOLD == 0) ? 3 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, const GemmParams p) {
@@ -833,7 +844,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                             if (fix1_rows) fold16(r, y0 + gq * GW + cc, prefetched ? &xg[cc / 4] : nullptr);
 #pragma unroll
                             for (int q = 0; q < 8; ++q) {
-                                __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * q]) * row_scale, __uint_as_float(r[2 * q + 1]) * row_scale);
+                                float e0 = __uint_as_float(r[2 * q]) * row_scale, e1 = __uint_as_float(r[2 * q + 1]) * row_scale;
+                                if constexpr (FOLD == 1) {
+                                    if (p.act) { e0 = gelu_tanh_of_bf16(e0); e1 = gelu_tanh_of_bf16(e1); }
+                                }
+                                __nv_bfloat162 v = __floats2bfloat162_rn(e0, e1);
                                 w[cc / 2 + q] = *reinterpret_cast<uint32_t*>(&v);
                             }
                         }
@@ -858,6 +873,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     if (scale_ssq != nullptr) {
 #pragma unroll
                         for (int q = 0; q < 16; ++q) r[q] = __float_as_uint(__uint_as_float(r[q]) * row_scale);
+                    }
+                    if constexpr (FOLD == 1) {
+                        if (p.act) {
+#pragma unroll
+                            for (int q = 0; q < 16; ++q) r[q] = __float_as_uint(gelu_tanh_of_bf16(__uint_as_float(r[q])));
+                        }
                     }
                 }
                 if (!alive || xr >= p.x_rows) {
@@ -1158,6 +1179,12 @@ static int gemm_tc_impl(const void* X, int x_rows, long long ldx, const void* Y,
                         int splits, int bn, int x_is_constant, int gated, int pair, int* err_flag, const PyreGemmFix* fx,
                         cudaStream_t stream) {
     if (x_rows <= 0 || y_rows <= 0) return 0;
+    // gated == 2: no gate, but gelu_tanh on the product, in the epilogue of a row store of one split (bf16 out)
+    const int act = gated == 2 ? 1 : 0;
+    if (act) {
+        gated = 0;
+        if (splits != 1 || out_f32 || stride_y != 1 || stride_x == 1 || (fx && fx->fix != 0)) return PYRE_ERR_BAD_ARG;
+    }
     if (fx && (fx->fix != 0 || fx->scale_ssq != nullptr) && stride_x != 1) {
         // row store (tokens on the rows): every thread of the epilogue owns a token row, so the row scale and the
         // residual fold (fix == 1) need no exchange between CTAs; one split, no gate with the fold, bf16 out
@@ -1210,7 +1237,7 @@ static int gemm_tc_impl(const void* X, int x_rows, long long ldx, const void* Y,
     p.x_rows = x_rows; p.y_rows = y_rows; p.K = K;
     p.k_blocks_per_split = (total_kb + splits - 1) / splits;
     p.stride_x = stride_x; p.stride_y = stride_y; p.split_stride = split_stride;
-    p.out = out; p.out_f32 = out_f32; p.x_is_constant = x_is_constant; p.err_flag = err_flag; p.gated = gated ? 1 : 0;
+    p.out = out; p.out_f32 = out_f32; p.x_is_constant = x_is_constant; p.err_flag = err_flag; p.gated = gated ? 1 : 0; p.act = act;
     p.scale_ssq = nullptr; p.scale_tiles = 0; p.scale_n = 0.f; p.scale_eps = 0.f; p.fix = 0; p.tile_counters = nullptr;
     p.resid = nullptr; p.norm_w = nullptr; p.h_out = nullptr; p.ssq_out = nullptr; p.bias = nullptr; p.cos_t = p.sin_t = nullptr;
     p.q_out = nullptr; p.kv_cache = nullptr; p.slot_mapping = nullptr; p.nh = p.nkv = p.hd = p.rot = p.page_size = 0; p.n_pages = 0;
@@ -1250,7 +1277,7 @@ static int gemm_tc_impl(const void* X, int x_rows, long long ldx, const void* Y,
         }
         // plain products (decode steps of 129-256 requests) run the variant without the folded work: few registers,
         // so that the next kernels' CTAs find room beside the draining pairs
-        const bool plain = p.fix == 0 && p.scale_ssq == nullptr;
+        const bool plain = p.fix == 0 && p.scale_ssq == nullptr && !p.act;
 #define GO2(BN_, ST_) return plain ? launch<BN_, ST_, false, 2, 0>(mx, my, p, grid2, stream) : launch<BN_, ST_, false, 2, 1>(mx, my, p, grid2, stream)
         switch (bn) {
             case 128: GO2(128, 8);
@@ -1266,7 +1293,7 @@ static int gemm_tc_impl(const void* X, int x_rows, long long ldx, const void* Y,
     dim3 grid((unsigned)ctas, 1, splits);
     // the plain products run the variant without that code: the weight stream always, the row store at the one width
     // that decode steps of 33-128 tokens use (96 registers, held there by its launch bounds, instead of 183: two of the attention's CTAs fit beside it)
-    const bool fold = p.fix != 0 || p.scale_ssq != nullptr;
+    const bool fold = p.fix != 0 || p.scale_ssq != nullptr || p.act;
 #define GO(BN_, ST_)                                                              \
     rc = !xc ? launch_rows<BN_, ST_>(mx, my, p, grid, stream, fold)                               \
         : fold ? launch<BN_, ST_, true, 1, 1>(mx, my, p, grid, stream)                              \

@@ -1103,6 +1103,28 @@ def norm_add(x: torch.Tensor, y: "torch.Tensor | PartialSums | DeferredProduct",
     return nxt
 
 
+def linear_act(x: torch.Tensor, w: torch.Tensor, kind: str) -> torch.Tensor:
+    """act(x W^T) in the activation dtype.  A bfloat16 prompt portion whose plan is a row store in one split gets
+    ``gelu_tanh`` in the product's epilogue (on the product rounded to bfloat16, so the result is that of the two
+    kernels); everything else runs the product and then ``activation``."""
+    if kind not in ACTIVATIONS:
+        raise UnsupportedSize(f"activation {kind!r}: implemented are {sorted(ACTIVATIONS)}")
+    if FUSE_ACTIVATION and kind == "gelu_tanh" and x.dtype == torch.bfloat16 and USE_TC_GEMM and tc_gemm_supported(x, w):
+        M, K = x.shape
+        N = w.shape[0]
+        weights_as_rows, bn, splits = tc_gemm_plan(M, N, K)
+        if M > 128 and not weights_as_rows and splits == 1 and N % 8 == 0:
+            out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+            pair = int(CTA_PAIRS and bn in (128, 160, 192, 208, 224, 256))
+            lib.call("pyre_gemm_tc", x.data_ptr(), M, x.stride(0), w.data_ptr(), N, w.stride(0), K, out.data_ptr(), 0,
+                     N, 1, 0, 1, bn, 0, 2, pair, device_error_flag(x.device).data_ptr(), None, _stream())
+            return out
+    return activation(materialize(linear(x, w)), kind)
+
+
+FUSE_ACTIVATION = True
+
+
 def activation(x: torch.Tensor, kind: str) -> torch.Tensor:
     """act(x) elementwise, fp32 arithmetic: ``silu`` or ``gelu_tanh`` (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))))."""
     _check(x, "x")

@@ -92,8 +92,7 @@ class DenseMLP(Part):
 
     def forward(self, ctx, h):
         with lib.section("up"):
-            z = ops.linear(h, self.w_up)
-        a = ops.activation(z, self.activation)
+            a = ops.linear_act(h, self.w_up, self.activation)
         with lib.section("down"):
             return ops.linear(a, self.w_down, partials_ok=True)
 

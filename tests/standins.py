@@ -107,6 +107,11 @@ def activation(x, kind):
     return torch.nn.functional.gelu(z, approximate="tanh").to(x.dtype)
 
 
+def linear_act(x, w, kind):
+    from pyre_b200.kernels import ops
+    return ops.activation(ops.materialize(ops.linear(x, w)), kind)
+
+
 def qk_norm_rope_write(proj, q_col, k_col, v_col, q_weight, k_weight, eps, cos, sin, cache_layer, slot_mapping, n_heads,
                        n_kv_heads, qk_dim, v_dim, row_dim, rotary_dim, page_size):
     T = proj.shape[0]
@@ -199,7 +204,7 @@ def install(monkeypatch) -> None:
     for name, fn in dict(embedding=embedding, add_rmsnorm=add_rmsnorm, add_residual=add_residual, rope_table=rope_table,
                          qkv_rope_write=qkv_rope_write, paged_attention_generic=paged_attention_generic,
                          sgemm_nt=sgemm_nt, silu_mul=silu_mul, sample=sample, feed_tokens=feed_tokens, cast_rows=cast_rows,
-                         norm_add=norm_add, activation=activation, qk_norm_rope_write=qk_norm_rope_write,
+                         norm_add=norm_add, activation=activation, linear_act=linear_act, qk_norm_rope_write=qk_norm_rope_write,
                          sigmoid_gate=sigmoid_gate, rmsnorm_gate=rmsnorm_gate, linear_attention=linear_attention).items():
         monkeypatch.setattr(ops, name, fn)
     monkeypatch.setattr(ops, "device_error_flag", lambda device: flag)

@@ -62,6 +62,24 @@ def test_activations(ops, dtype):
         ops.activation(z, "relu")
 
 
+@pytest.mark.parametrize("M,N,K", [(300, 512, 256), (2048, 1000, 320), (129, 2048, 64), (640, 264, 1024), (8, 512, 256), (200, 96, 92)])
+def test_product_with_gelu_in_its_epilogue(ops, M, N, K):
+    """act(x W^T) of a prompt portion with the activation in the product's epilogue gives what the product followed
+    by the activation kernel gives (the activation reads the product rounded to bfloat16 either way); few tokens,
+    split products and sizes the tensor-core product does not take run the two kernels."""
+    g = torch.Generator(device="cuda").manual_seed(M + N)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda", generator=g) * K ** -0.5 * 2).to(torch.bfloat16)
+    got = ops.linear_act(x, w, "gelu_tanh")
+    two = ops.activation(ops.materialize(ops.linear(x, w)), "gelu_tanh")
+    want = MP.gelu_tanh((x.double() @ w.double().t()).to(torch.bfloat16).double())
+    assert got.shape == (M, N) and got.dtype == torch.bfloat16
+    close(got, want, torch.bfloat16, "fused")
+    close(two, want, torch.bfloat16, "two kernels")
+    assert (got.float() - two.float()).abs().max() <= 2 ** -6 * two.float().abs().max()
+    ops.check_device_errors()
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nh,nkv,dk,dv,rot,page,write", [(4, 2, 32, 16, 8, 16, True), (5, 5, 24, 40, 0, 8, True),
                                                          (3, 1, 64, 64, 64, 4, True), (6, 2, 80, 112, 32, 16, True),
