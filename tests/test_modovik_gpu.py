@@ -90,7 +90,7 @@ def test_head_norm_rotation_and_paged_write(ops, dtype, nh, nkv, dk, dv, rot, pa
     T, eps, base = 23, 1e-5, 10000.0
     D = ops.attention_row_dim(dk, dv, dtype)
     g = torch.Generator(device="cuda").manual_seed(nh * dk + dv)
-    extra = 7      # columns that belong to something else (a gate) after the values
+    extra = 8 if nh % 2 == 0 else 7      # columns that belong to something else (a gate) after the values; 7: rows that no vector access fits
     W = nh * dk + (nkv * (dk + dv) if write else 0) + extra
     proj = (torch.randn(T, W, device="cuda", generator=g) * 2).to(dtype)
     qw = 1 + 0.2 * torch.randn(dk, device="cuda", generator=g)
