@@ -2,8 +2,8 @@
 and slots of fixed-size state.
 
 Groups.  Layers whose mixers need the same of the cache (``PagedKVSpec``: heads, head
-size, window) form a group.  A group has its own pool ``[layers, pages, 2, kv_heads,
-page_size, head_dim]`` (one page number addresses the same page in every layer of the
+size, window, planes) form a group.  A group has its own pool ``[layers, pages, planes, kv_heads,
+page_size, head_dim]`` (two planes, keys and values, or one plane of rows that serve as both) (one page number addresses the same page in every layer of the
 group, as in the reference, pyre/paged_cache.py:107), its own allocator and its own
 block table per request.  A group with a window gives a page back as soon as every
 position in it lies before the window of any token still to come; a group without one
@@ -71,7 +71,7 @@ class PagedGroup:
         self.scratch_page = num_pages
         self.pool = None
         if allocate_pool:
-            self.pool = torch.zeros((n_layers, num_pages + 1, 2, spec.n_kv_heads, page_size, spec.head_dim),
+            self.pool = torch.zeros((n_layers, num_pages + 1, getattr(spec, "planes", 2), spec.n_kv_heads, page_size, spec.head_dim),
                                     dtype=dtype, device=device)
         self.poison = False
 

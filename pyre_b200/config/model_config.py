@@ -258,3 +258,149 @@ class ModovikConfig(ModelConfig):
             layers.append({"type": L.kind, "mixer": mixer, "mlp": {"kind": "dense", "ff": L.ff} if L.ff else None})
         return {"architecture": self.architecture, "vocab": self.vocab, "width": self.width,
                 "norm": {"eps": self.norm_eps}, "layers": layers}
+
+
+@dataclass(frozen=True)
+class PivinexLayer:
+    """One layer of a Pivinex model: a latent-attention mixer (its sizes) and its feed-forward: ``mlp_kind`` "dense"
+    (gated, ``ff`` wide), "moe" (``experts`` gated experts of ``ff`` plus ``identity`` router outputs without weights,
+    ``top`` per token, weights scaled by ``router_scale``) or "" (none)."""
+
+    kind: str
+    heads: int
+    dim: int                       # unrotated query/key entries per head
+    rot_dim: int                   # rotated query/key entries per head (the key's are shared by the heads)
+    vdim: int                      # value entries per head
+    q_rank: int                    # size of the query latent
+    kv_rank: int                   # size of the cached key/value latent
+    scale: float                   # factor on q . k
+    window: int = 0                # a position sees itself and window - 1 before it (0: all)
+    rot_dims: int = 0              # leading entries of the rotated part that are rotated
+    rot_base: float = 10000.0
+    mlp_kind: str = ""
+    ff: int = 0
+    experts: int = 0
+    identity: int = 0
+    top: int = 0
+    router_scale: float = 1.0
+
+
+@dataclass(frozen=True)
+class PivinexConfig(ModelConfig):
+    """A Pivinex decoder: an embedding followed by a layer norm; layers that read ONE layer norm and add
+    ``residual_mult`` times (mixer and feed-forward, each with a gain per feature) to the stream; a span of layers
+    ``loop_start .. loop_stop - 1`` that runs ``loop_times`` times in a row with the same weights, each pass with a
+    cache of its own, the embedding's output added to the stream before every pass but the first; a final layer norm
+    and a head.  ``config.json`` keys: ``vocab``, ``width``, ``norm.eps``, ``residual_mult``, ``loop: {start, stop,
+    times}`` (optional) and ``layers``, a list of ``{"type": "latent_attention", "mixer": {heads, dim, rot_dim, vdim,
+    q_rank, kv_rank, scale, mask: {size}, rot: {dims, base}}, "mlp": {"kind": "dense", "ff"} | {"kind": "moe", "expert":
+    {"ff"}, "router": {experts, identity, top, scale}} | null}``."""
+
+    architecture: ClassVar[str] = "Pivinex"
+
+    vocab: int
+    width: int
+    norm_eps: float
+    residual_mult: float
+    layers: tuple
+    loop_start: int = 0
+    loop_stop: int = 0
+    loop_times: int = 1
+
+    def __post_init__(self):
+        _positive("vocab", self.vocab)
+        _positive("width", self.width)
+        if not self.norm_eps > 0:
+            raise ConfigError(f"config.json: norm.eps must be positive, got {self.norm_eps}")
+        if not self.layers:
+            raise ConfigError("config.json: layers is empty")
+        if not (0 <= self.loop_start <= self.loop_stop <= len(self.layers)) or self.loop_times < 1:
+            raise ConfigError(f"config.json: loop {{start: {self.loop_start}, stop: {self.loop_stop}, times: {self.loop_times}}} "
+                              f"must name a span of the {len(self.layers)} layers and run it at least once")
+        for i, L in enumerate(self.layers):
+            where = f"config.json: layers[{i}]"
+            if L.kind != "latent_attention":
+                raise ConfigError(f"{where}.type {L.kind!r}: known is 'latent_attention'")
+            for name in ("heads", "dim", "vdim", "q_rank", "kv_rank"):
+                if getattr(L, name) <= 0:
+                    raise ConfigError(f"{where}.mixer.{name} must be positive")
+            if L.rot_dim < 0 or L.rot_dims < 0 or L.rot_dims % 2 or L.rot_dims > L.rot_dim:
+                raise ConfigError(f"{where}.mixer.rot.dims ({L.rot_dims}) must be even and at most rot_dim ({L.rot_dim})")
+            if L.rot_dims and not L.rot_base > 0:
+                raise ConfigError(f"{where}.mixer.rot.base must be positive")
+            if L.window < 0:
+                raise ConfigError(f"{where}.mixer.mask.size must be positive")
+            if L.mlp_kind not in ("", "dense", "moe"):
+                raise ConfigError(f"{where}.mlp.kind {L.mlp_kind!r}: known are 'dense' and 'moe'")
+            if L.mlp_kind and L.ff <= 0:
+                raise ConfigError(f"{where}.mlp: ff must be positive")
+            if L.mlp_kind == "moe" and (L.experts <= 0 or L.identity < 0 or not 0 < L.top <= L.experts + L.identity):
+                raise ConfigError(f"{where}.mlp.router: {L.experts} experts + {L.identity} identity cannot give top {L.top}")
+
+    @classmethod
+    def from_dict(cls, raw: dict[str, Any]) -> "PivinexConfig":
+        norm = raw.get("norm")
+        if not isinstance(norm, dict):
+            raise ConfigError("config.json: required key 'norm' (with 'eps') is missing")
+        layers_raw = raw.get("layers")
+        if not isinstance(layers_raw, (list, tuple)):
+            raise ConfigError("config.json: required key 'layers' is missing")
+        layers = []
+        for i, entry in enumerate(layers_raw):
+            where = f"layers[{i}]"
+            if not isinstance(entry, dict) or not isinstance(entry.get("mixer"), dict):
+                raise ConfigError(f"config.json: {where} needs 'type' and 'mixer'")
+            m = entry["mixer"]
+            rot = m.get("rot") or {}
+            mask = m.get("mask") or {}
+            rot_dim = int(m.get("rot_dim") or 0)
+            fields = dict(kind=str(entry.get("type")), heads=_require(m, "heads"), dim=_require(m, "dim"), rot_dim=rot_dim,
+                          vdim=_require(m, "vdim"), q_rank=_require(m, "q_rank"), kv_rank=_require(m, "kv_rank"),
+                          scale=_require(m, "scale", float), window=int(mask.get("size") or 0),
+                          rot_dims=int(rot.get("dims", rot_dim)), rot_base=float(rot.get("base", 10000.0)))
+            mlp = entry.get("mlp")
+            if mlp is not None:
+                if not isinstance(mlp, dict):
+                    raise ConfigError(f"config.json: {where}.mlp must be an object or null")
+                kind = str(mlp.get("kind", "dense"))
+                fields["mlp_kind"] = kind
+                if kind == "moe":
+                    expert, router = mlp.get("expert"), mlp.get("router")
+                    if not isinstance(expert, dict) or not isinstance(router, dict):
+                        raise ConfigError(f"config.json: {where}.mlp needs 'expert' and 'router'")
+                    fields.update(ff=_require(expert, "ff"), experts=_require(router, "experts"),
+                                  identity=int(router.get("identity") or 0), top=_require(router, "top"),
+                                  router_scale=float(router.get("scale", 1.0)))
+                else:
+                    fields["ff"] = _require(mlp, "ff")
+            layers.append(PivinexLayer(**fields))
+        loop = raw.get("loop") or {}
+        start = int(loop.get("start", 0))
+        return cls(vocab=_require(raw, "vocab"), width=_require(raw, "width"), norm_eps=_require(norm, "eps", float),
+                   residual_mult=float(raw.get("residual_mult", 1.0)), layers=tuple(layers), loop_start=start,
+                   loop_stop=int(loop.get("stop", start)), loop_times=int(loop.get("times", 1)))
+
+    def to_dict(self) -> dict[str, Any]:
+        layers = []
+        for L in self.layers:
+            mixer = {"heads": L.heads, "dim": L.dim, "rot_dim": L.rot_dim, "vdim": L.vdim, "q_rank": L.q_rank,
+                     "kv_rank": L.kv_rank, "scale": L.scale, "rot": {"dims": L.rot_dims, "base": L.rot_base}}
+            if L.window:
+                mixer["mask"] = {"size": L.window}
+            mlp = None
+            if L.mlp_kind == "dense":
+                mlp = {"kind": "dense", "ff": L.ff}
+            elif L.mlp_kind == "moe":
+                mlp = {"kind": "moe", "expert": {"ff": L.ff},
+                       "router": {"experts": L.experts, "identity": L.identity, "top": L.top, "scale": L.router_scale}}
+            layers.append({"type": L.kind, "mixer": mixer, "mlp": mlp})
+        return {"architecture": self.architecture, "vocab": self.vocab, "width": self.width, "norm": {"eps": self.norm_eps},
+                "residual_mult": self.residual_mult,
+                "loop": {"start": self.loop_start, "stop": self.loop_stop, "times": self.loop_times}, "layers": layers}
+
+    def layer_order(self) -> list:
+        """(layer index, first layer of a repeated pass?) in the order the layers run."""
+        order = [(i, False) for i in range(self.loop_start)]
+        for rep in range(self.loop_times):
+            order += [(i, rep > 0 and i == self.loop_start) for i in range(self.loop_start, self.loop_stop)]
+        return order + [(i, False) for i in range(self.loop_stop, len(self.layers))]

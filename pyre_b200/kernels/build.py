@@ -37,6 +37,9 @@ LIBRARIES = {
     "attention_mma_noalloc": "attention_mma_noalloc.cu",
     "blockops": "blockops.cu",
     "linear_attention": "linear_attention.cu",
+    "parallel_block": "parallel_block.cu",
+    "latent_attention": "latent_attention.cu",
+    "grouped": "grouped.cu",
 }
 
 HEADERS = ["common.cuh", "attention_mma_noalloc.h"]

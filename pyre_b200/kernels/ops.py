@@ -92,9 +92,11 @@ class DeferredProduct:
             return gemm_tc(self.x, self.w, self.dtype, reduce=False)
 
 
-def materialize(t: "torch.Tensor | PartialSums | DeferredProduct | ScaledRows") -> torch.Tensor:
+def materialize(t: "torch.Tensor | PartialSums | DeferredProduct | ScaledRows | ScaledSum") -> torch.Tensor:
     """A plain tensor in the activation dtype from a tensor or any of the lazy forms a branch output or a
     norm's output may take."""
+    if isinstance(t, ScaledSum):
+        return t.tensor()
     if isinstance(t, DeferredProduct):
         t = t.partials()
     if isinstance(t, ScaledRows):
@@ -1290,3 +1292,307 @@ def attention_row_dim(qk_dim: int, v_dim: int, dtype: torch.dtype) -> int:
     if d > 256:
         raise UnsupportedSize(f"heads of {qk_dim} / {v_dim} dims: the attention kernels take up to 256")
     return d
+
+
+# ---------------------------------------------------------------------------------- layers whose branches share one norm
+class ScaledSum:
+    """The branch outputs of a layer that adds all of them to the stream at once, each with a gain per feature:
+    ``sum_k scale_k * term_k``, not formed yet.  ``terms``: one or two of (branch output, fp32 gain [H]); a branch
+    output is a tensor [T, H] in the activation dtype, an fp32 tensor [T, H] (taken as one part of a split
+    product) or ``PartialSums``.  A norm that knows this type adds the terms to the fp32 stream in its own kernel
+    (``add_layernorm``); anything else calls ``materialize``."""
+
+    def __init__(self, terms, dtype: torch.dtype):
+        if not 1 <= len(terms) <= 2:
+            raise ValueError("a ScaledSum holds one or two terms")
+        self.terms = [(materialize(t) if isinstance(t, (DeferredProduct, ScaledRows)) else t, s) for t, s in terms]
+        self.dtype = dtype
+
+    @property
+    def shape(self):
+        return tuple(self.terms[0][0].shape)
+
+    def _args(self, act_dtype):
+        """Per term (tensor pointer, parts pointer, number of parts, gain pointer), two terms, and the parts' stride."""
+        out, stride = [], 0
+        T, H = self.shape
+        for t, s in self.terms:
+            _check(s, "gain", torch.float32, 1)
+            if s.shape[0] != H:
+                raise ValueError(f"a gain of {s.shape[0]} entries for rows of {H}")
+            if isinstance(t, PartialSums):
+                out += [None, t.parts.data_ptr(), t.n, s.data_ptr()]
+                stride = T * H
+            elif t.dtype == torch.float32 and act_dtype != torch.float32:
+                _check(t, "branch output", torch.float32, 2)
+                out += [None, t.data_ptr(), 1, s.data_ptr()]
+                stride = T * H
+            else:
+                _check(t, "branch output", act_dtype, 2)
+                out += [t.data_ptr(), None, 0, s.data_ptr()]
+            if tuple(t.shape) != (T, H):
+                raise ValueError("the branch outputs differ in shape")
+        if len(self.terms) == 1:
+            out += [None, None, 0, None]
+        return out, stride
+
+    def tensor(self) -> torch.Tensor:
+        T, H = self.shape
+        args, stride = self._args(self.dtype)
+        out = torch.empty((T, H), dtype=self.dtype, device=self.terms[0][1].device)
+        lib.call("pyre_scaled_sum", *args, stride, out.data_ptr(), T, H, _dt(self.dtype), _stream())
+        return out
+
+
+def add_layernorm(x: torch.Tensor, delta: "ScaledSum | torch.Tensor | PartialSums | None", weight: torch.Tensor, eps: float,
+                  out_dtype: torch.dtype, rows: "torch.Tensor | None" = None, update_x: bool = True,
+                  act_dtype: "torch.dtype | None" = None) -> torch.Tensor:
+    """out[r] = layernorm(x[src] + delta[src]) * weight with src = rows[r] (or r): the mean is taken off, the
+    variance is the mean squared deviation, no bias.  ``x`` is the fp32 residual stream [T, H]; with ``update_x``
+    (and no ``rows``) the sum is written back to it.  ``delta``: a ``ScaledSum`` (each term times its gain), a
+    plain branch output or partial sums (gain one), or None.  ``out_dtype`` float32 with bfloat16 activations
+    (``act_dtype``) gives the normalised rows in fp32: a norm applied to the stream itself."""
+    _check(x, "x", torch.float32, 2)
+    _check(weight, "weight", torch.float32, 1)
+    T, H = x.shape
+    act = act_dtype or out_dtype
+    if weight.shape[0] != H:
+        raise ValueError(f"norm weight has {weight.shape[0]} entries, rows have {H}")
+    if H * 4 > 48 * 1024:
+        raise UnsupportedSize(f"layer norm over rows of {H}: the kernel holds a row of at most 12,288 in shared memory")
+    if delta is not None and not isinstance(delta, ScaledSum):
+        delta = ScaledSum([(delta, _ones(H, x.device))], act)
+    args, stride = ([None, None, 0, None] * 2, 0)
+    if delta is not None:
+        if delta.shape != (T, H):
+            raise ValueError(f"delta shape {delta.shape} != x shape {(T, H)}")
+        args, stride = delta._args(act)
+    n_rows = T
+    if rows is not None:
+        _check(rows, "rows", torch.int32, 1)
+        n_rows, update_x = rows.shape[0], False
+    out = torch.empty((n_rows, H), dtype=out_dtype, device=x.device)
+    lib.call("pyre_add_layernorm", x.data_ptr(), *args, stride, weight.data_ptr(), out.data_ptr(),
+             int(out_dtype == torch.float32 and act != torch.float32), _ptr(rows), n_rows, H, float(eps),
+             int(bool(update_x and delta is not None)), _dt(act), _stream())
+    return out
+
+
+_ones_cache: dict = {}
+
+
+def _ones(n: int, device) -> torch.Tensor:
+    key = (n, str(device))
+    t = _ones_cache.get(key)
+    if t is None:
+        t = _ones_cache[key] = torch.ones(n, dtype=torch.float32, device=device)
+    return t
+
+
+def act_mul(gate_up: torch.Tensor, kind: str) -> torch.Tensor:
+    """out[t, i] = act(gate_up[t, i]) * gate_up[t, I + i] for rows [gates | ups]; ``kind`` as in ``ACTIVATIONS``."""
+    _check(gate_up, "gate_up", dim=2)
+    if kind not in ACTIVATIONS:
+        raise UnsupportedSize(f"activation {kind!r}: implemented are {sorted(ACTIVATIONS)}")
+    T, two_i = gate_up.shape
+    if two_i % 2:
+        raise ValueError("gate_up must have an even number of columns")
+    out = torch.empty((T, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    lib.call("pyre_act_mul", gate_up.data_ptr(), out.data_ptr(), T, two_i // 2, ACTIVATIONS[kind], _dt(gate_up.dtype), _stream())
+    return out
+
+
+# ---------------------------------------------------------------------------------- attention over a cache of latent rows
+LATENT_MAX_RANK = 512
+
+
+def latent_prepare(proj: "torch.Tensor | PartialSums", q_col: int, q_rank: int, c_col: int, rank: int, rope: int, rot: int,
+                   wq: "torch.Tensor | None", wc: torch.Tensor, eps: float, cos: "torch.Tensor | None", sin: "torch.Tensor | None",
+                   cache_layer: "torch.Tensor | None", slot_mapping: "torch.Tensor | None", page_size: int,
+                   act_dtype: torch.dtype) -> "torch.Tensor | None":
+    """From a token's down-projections ``proj`` [T, W] (columns ``q_col``: the query latent of ``q_rank`` entries,
+    0 for none; ``c_col``: the key/value latent of ``rank`` entries followed by the shared key part of ``rope``):
+    returns rmsnorm(query latent) * wq [T, q_rank] and writes [rmsnorm(latent) * wc | rotate(key part)] to the
+    token's row of ``cache_layer`` [pages, 1, 1, page_size, row].  The rotation turns neighbouring pairs of the
+    first ``rot`` entries by the angles whose cos/sin are given [T, rot / 2]."""
+    parts, n_parts, stride, tensor = None, 0, 0, None
+    if isinstance(proj, PartialSums):
+        parts, n_parts, stride = proj.parts, proj.n, proj.parts[0].numel()
+        T, W = proj.shape
+        device = proj.parts.device
+    else:
+        _check(proj, "proj", act_dtype, 2)
+        tensor, (T, W), device = proj, proj.shape, proj.device
+    if q_col < 0 or q_col + q_rank > W or c_col < 0 or c_col + rank + rope > W:
+        raise ValueError("the latents do not lie inside the projection row")
+    if rot % 2 or not 0 <= rot <= rope:
+        raise UnsupportedSize(f"rotated dims ({rot}) must be even and at most the rotated key part ({rope})")
+    _check(wc, "wc", torch.float32, 1)
+    if wc.shape[0] != rank or (q_rank and (wq is None or wq.shape[0] != q_rank)):
+        raise ValueError("a norm weight does not match its latent")
+    if rot:
+        _check(cos, "cos", torch.float32, 2)
+        _check(sin, "sin", torch.float32, 2)
+        if tuple(cos.shape) != (T, rot // 2) or tuple(sin.shape) != (T, rot // 2):
+            raise ValueError(f"cos/sin must be [{T}, {rot // 2}], got {tuple(cos.shape)}")
+    row = n_pages = 0
+    if cache_layer is not None:
+        _check(cache_layer, "cache_layer", act_dtype, 5)
+        row, n_pages = cache_layer.shape[4], cache_layer.shape[0]
+        if tuple(cache_layer.shape[1:4]) != (1, 1, page_size) or row < rank + rope:
+            raise ValueError(f"cache layer shape {tuple(cache_layer.shape)} does not match [pages, 1, 1, {page_size}, >= {rank + rope}]")
+        _check(slot_mapping, "slot_mapping", torch.int32, 1)
+        if slot_mapping.shape[0] != T:
+            raise ValueError("slot_mapping must have one entry per token")
+    cq = torch.empty((T, q_rank), dtype=act_dtype, device=device) if q_rank else None
+    lib.call("pyre_latent_prepare", _ptr(tensor), _ptr(parts), n_parts, stride, W, int(q_col), int(q_rank), int(c_col), int(rank),
+             int(rope), int(rot), _ptr(wq), wc.data_ptr(), float(eps), _ptr(cos) if rot else None, _ptr(sin) if rot else None,
+             _ptr(cq), _ptr(cache_layer), _ptr(slot_mapping) if cache_layer is not None else None, T, max(row, rank + rope),
+             n_pages, int(page_size), _dt(act_dtype), device_error_flag(device).data_ptr(), _stream())
+    return cq
+
+
+def latent_rotate_q(q: torch.Tensor, qa: torch.Tensor, cos, sin, n_heads: int, dq: int, rope: int, rot: int, rank: int) -> None:
+    """qa[t, h, rank + i] = rotate(q[t, h, dq + i]) for i < rope (zeros beyond): the rotated tail of the absorbed
+    query rows ``qa`` [T, n_heads, row]; ``q`` [T, n_heads * (dq + rope)]."""
+    _check(q, "q", dim=2)
+    _check(qa, "qa", q.dtype, 3)
+    T, row = q.shape[0], qa.shape[2]
+    if q.shape[1] != n_heads * (dq + rope) or tuple(qa.shape[:2]) != (T, n_heads) or row < rank + rope:
+        raise ValueError("q or qa do not match the head sizes")
+    lib.call("pyre_latent_rotate_q", q.data_ptr(), qa.data_ptr(), _ptr(cos) if rot else None, _ptr(sin) if rot else None, T,
+             n_heads, int(dq), int(rope), int(rot), int(rank), row, _dt(q.dtype), _stream())
+
+
+def latent_attention_exact(qa: torch.Tensor, cache_layer: torch.Tensor, block_table: torch.Tensor, seq_of_token: torch.Tensor,
+                           positions: torch.Tensor, rank: int, rope: int, scale: float, window: "int | None") -> torch.Tensor:
+    """Exact fp32-arithmetic attention of absorbed queries ``qa`` [T, nh, row] over the latent rows of their
+    sequences' pages: score = qa . row[: rank + rope] * scale, output = sum of probabilities times row[: rank];
+    returns [T, nh, rank]."""
+    _check(qa, "qa", dim=3)
+    _check(cache_layer, "cache_layer", qa.dtype, 5)
+    _check(block_table, "block_table", torch.int32, 2)
+    _check(seq_of_token, "seq_of_token", torch.int32, 1)
+    _check(positions, "positions", torch.int32, 1)
+    T, nh, row = qa.shape
+    page_size = cache_layer.shape[3]
+    if tuple(cache_layer.shape[1:]) != (1, 1, page_size, row) or row < rank + rope:
+        raise ValueError(f"cache layer shape {tuple(cache_layer.shape)} does not match rows of {row}")
+    if rank > LATENT_MAX_RANK or (rank + rope) * 16 > 48 * 1024:
+        raise UnsupportedSize(f"latent rows of {rank} + {rope}: the kernel takes latents up to {LATENT_MAX_RANK}")
+    out = torch.empty((T, nh, rank), dtype=qa.dtype, device=qa.device)
+    lib.call("pyre_latent_attention_exact", qa.data_ptr(), cache_layer.data_ptr(), out.data_ptr(), block_table.data_ptr(),
+             block_table.stride(0), seq_of_token.data_ptr(), positions.data_ptr(), T, nh, int(rank), int(rope), row, page_size,
+             int(window or 0), float(scale), _dt(qa.dtype), cache_layer.shape[0], device_error_flag(qa.device).data_ptr(), _stream())
+    return out
+
+
+# ---------------------------------------------------------------------------------- one weight matrix per group
+USE_GROUPED_MMA = True
+
+
+def _grouped_mma_ok(x: torch.Tensor, w: torch.Tensor, x_row_stride: int, x_group_stride: int, K: int) -> int:
+    return int(USE_GROUPED_MMA and x.dtype == torch.bfloat16 and K % 8 == 0 and x_row_stride % 8 == 0
+               and x_group_stride % 8 == 0 and (w.shape[1] * w.shape[2]) % 8 == 0 and x.data_ptr() % 16 == 0
+               and w.data_ptr() % 16 == 0)
+
+
+def headwise_linear(x: torch.Tensor, w: torch.Tensor, out: "torch.Tensor | None" = None) -> torch.Tensor:
+    """out[t, h, :N] = x[t, h, :K] . w[h]^T for ``x`` [T, H, >= K] and ``w`` [H, N, K]: a product per head.  ``out``
+    [T, H, >= N] may be given (rows wider than N keep their other columns); else [T, H, N] is returned."""
+    _check(x, "x", dim=3)
+    _check(w, "w", x.dtype, 3)
+    T, H, xs = x.shape
+    _, N, K = w.shape
+    if w.shape[0] != H or xs < K:
+        raise ValueError(f"x {tuple(x.shape)} and w {tuple(w.shape)} do not match head by head")
+    if out is None:
+        out = torch.empty((T, H, N), dtype=x.dtype, device=x.device)
+    else:
+        _check(out, "out", x.dtype, 3)
+        if tuple(out.shape[:2]) != (T, H) or out.shape[2] < N:
+            raise ValueError("out does not match the heads")
+    lib.call("pyre_grouped_linear", x.data_ptr(), H * xs, xs, w.data_ptr(), N * K, out.data_ptr(), H * out.shape[2], out.shape[2],
+             None, None, None, T, N, K, H, 0, 0, _dt(x.dtype), _grouped_mma_ok(x, w, H * xs, xs, K), _stream())
+    return out
+
+
+def expert_linear(x: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, src: "torch.Tensor | None", n_places: int,
+                  out_dtype: "torch.dtype | None" = None) -> torch.Tensor:
+    """out[p] = x[src[p]] . w[e]^T for every sorted place p of expert e (``offsets`` [E + 1] on the device; places
+    beyond ``offsets[E]`` are not written); ``x`` [rows, K], ``w`` [E, N, K]; ``src`` None: place p reads row p.
+    Returns [n_places, N] in ``out_dtype`` (the activation dtype, or float32)."""
+    _check(x, "x", dim=2)
+    _check(w, "w", x.dtype, 3)
+    _check(offsets, "offsets", torch.int32, 1)
+    E, N, K = w.shape
+    if x.shape[1] != K or offsets.shape[0] != E + 1:
+        raise ValueError("x, w and offsets do not match")
+    if src is not None:
+        _check(src, "src", torch.int32, 1)
+    out_dtype = out_dtype or x.dtype
+    if out_dtype not in (x.dtype, torch.float32):
+        raise ValueError("the result is in the activation dtype or float32")
+    out = torch.empty((n_places, N), dtype=out_dtype, device=x.device)
+    lib.call("pyre_grouped_linear", x.data_ptr(), K, 0, w.data_ptr(), N * K, out.data_ptr(), N, 0, offsets.data_ptr(), _ptr(src),
+             None, 0, N, K, E, int(n_places), int(out_dtype == torch.float32), _dt(x.dtype), _grouped_mma_ok(x, w, K, 0, K), _stream())
+    return out
+
+
+def route(h: torch.Tensor, w: torch.Tensor, correction: "torch.Tensor | None", top: int, scale: float):
+    """Router of a routed feed-forward: fp32 logits w h over all router outputs, softmax scores s; the ``top``
+    outputs with the largest s + correction are chosen (lowest index on ties), weights s * scale.
+    Returns (idx int32 [T, top], weight fp32 [T, top])."""
+    _check(h, "h", dim=2)
+    _check(w, "w", torch.float32, 2)
+    T, H = h.shape
+    n_out = w.shape[0]
+    if w.shape[1] != H or not 0 < top <= n_out:
+        raise ValueError("router weight or top do not match")
+    if correction is not None:
+        _check(correction, "correction", torch.float32, 1)
+        if correction.shape[0] != n_out:
+            raise ValueError("one correction per router output")
+    if n_out * 8 > 48 * 1024:
+        raise UnsupportedSize(f"{n_out} router outputs: the kernel takes up to 6,144")
+    idx = torch.empty((T, top), dtype=torch.int32, device=h.device)
+    weight = torch.empty((T, top), dtype=torch.float32, device=h.device)
+    lib.call("pyre_route", h.data_ptr(), w.data_ptr(), _ptr(correction), idx.data_ptr(), weight.data_ptr(), T, H, n_out, int(top),
+             float(scale), _dt(h.dtype), _stream())
+    return idx, weight
+
+
+def group_pairs(idx: torch.Tensor, n_experts: int):
+    """Sort the (token, choice) pairs ``idx`` [T, top] by expert; outputs >= ``n_experts`` get no place.
+    Returns (offsets int32 [n_experts + 1], place_of int32 [T, top], src int32 [T * top])."""
+    _check(idx, "idx", torch.int32, 2)
+    T, top = idx.shape
+    if n_experts * 4 > 48 * 1024:
+        raise UnsupportedSize(f"{n_experts} experts: the kernel takes up to 12,288")
+    offsets = torch.empty(n_experts + 1, dtype=torch.int32, device=idx.device)
+    place_of = torch.empty((T, top), dtype=torch.int32, device=idx.device)
+    src = torch.empty(T * top, dtype=torch.int32, device=idx.device)
+    lib.call("pyre_group_pairs", idx.data_ptr(), T * top, top, int(n_experts), offsets.data_ptr(), place_of.data_ptr(),
+             src.data_ptr(), _stream())
+    return offsets, place_of, src
+
+
+def combine_pairs(y: torch.Tensor, h: torch.Tensor, place_of: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """out[t] = sum_k weight[t, k] * (y[place_of[t, k]], or h[t] where the place is -1), fp32 [T, H]."""
+    _check(y, "y", torch.float32, 2)
+    _check(h, "h", dim=2)
+    _check(place_of, "place_of", torch.int32, 2)
+    _check(weight, "weight", torch.float32, 2)
+    T, H = h.shape
+    if y.shape[1] != H or place_of.shape != weight.shape or place_of.shape[0] != T:
+        raise ValueError("y, h, place_of and weight do not match")
+    out = torch.empty((T, H), dtype=torch.float32, device=h.device)
+    lib.call("pyre_combine_pairs", y.data_ptr(), h.data_ptr(), place_of.data_ptr(), weight.data_ptr(), out.data_ptr(), T, H,
+             place_of.shape[1], _dt(h.dtype), _stream())
+    return out
+
+
+def latent_attention(ctx, qa: torch.Tensor, cache_layer: torch.Tensor, block_table: torch.Tensor, rank: int, rope: int,
+                     scale: float, window: "int | None") -> torch.Tensor:
+    """Attention of a whole step's absorbed queries over their sequences' latent rows; [T, nh, rank]."""
+    return latent_attention_exact(qa, cache_layer, block_table, ctx.seq_of_token, ctx.positions, rank, rope, scale, window)

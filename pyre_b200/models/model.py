@@ -107,7 +107,7 @@ class Model:
                 st_group = st_specs.index(sspec)
                 st_layer = st_layers[st_group]
                 st_layers[st_group] += 1
-            calls.append(BoundCall(n, call.block, kv_group, kv_layer, call.write, st_group, st_layer))
+            calls.append(BoundCall(n, call.block, kv_group, kv_layer, call.write, st_group, st_layer, bool(call.add_embedding)))
         kv_groups = [KVGroup(s, n) for s, n in zip(kv_specs, kv_layers)]
         state_groups = [StateGroup(s, n) for s, n in zip(st_specs, st_layers)]
         return calls, kv_groups, state_groups
@@ -149,7 +149,12 @@ class Model:
             raise RuntimeError("the model has no weights: call load_weights or init_random first")
         x = self.embed.forward(ctx)
         pending = None
+        # blocks update the stream in place: an entry that adds the embedding's output again needs a copy of it
+        fed = x.clone() if any(call.add_embedding for call in self.calls) else None
         for call in self.calls:
+            if call.add_embedding:
+                from ..kernels import ops
+                ops.add_residual(x, fed)      # a branch output still pending is added by the block's norm, as ever
             x, pending = self.blocks[call.block].forward(ctx, x, pending, call)
         if ctx.num_logit_rows == 0:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)

@@ -15,11 +15,15 @@ class LayerCall:
     the same weights run twice).
     ``cache``: identifier of the cache layer this entry uses; None = a layer of its own.
     Two entries with the same identifier share keys and values: the first one in the
-    schedule writes them, later ones need ``write=False`` and read them."""
+    schedule writes them, later ones need ``write=False`` and read them.
+    ``add_embedding``: before this entry runs, the embedding's output (the stream as it was before the first
+    entry) is added to the stream: a model that runs a span of its layers several times feeds its input in
+    again at the start of every repeat."""
 
     block: int
     cache: "int | str | None" = None
     write: bool = True
+    add_embedding: bool = False
 
 
 @dataclass

@@ -69,15 +69,18 @@ class PartSpec:
 class PagedKVSpec:
     """What an attention-like mixer needs from the paged cache: per token and layer,
     keys and values of ``n_kv_heads * head_dim`` elements each.  ``window``: only the
-    last ``window`` positions are ever read (None = all), so older pages may be given back."""
+    last ``window`` positions are ever read (None = all), so older pages may be given back.
+    ``planes``: 2 = a plane of keys and a plane of values per page; 1 = one plane of rows that serve as both (a
+    cache of latent rows from which keys and values are derived)."""
 
     n_kv_heads: int
     head_dim: int
     window: int | None = None
+    planes: int = 2
 
     def bytes_per_token(self, element_size: int) -> int:
         """Bytes of one token's keys and values in one layer of the group."""
-        return 2 * self.n_kv_heads * self.head_dim * element_size
+        return self.planes * self.n_kv_heads * self.head_dim * element_size
 
     def tokens_held(self, step_tokens: int) -> "int | None":
         """The most tokens of one request whose pages are held at a time, when a step brings it at most
@@ -144,6 +147,7 @@ class BoundCall:
     kv_write: bool = True      # False: read what another call wrote
     state_group: int | None = None
     state_layer: int = 0
+    add_embedding: bool = False   # the embedding's output is added to the stream before this entry runs
 
 
 class Part:

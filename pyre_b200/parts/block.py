@@ -1,5 +1,5 @@
-"""Arrangements of a layer's parts: the pre-norm residual block (pyre/model.py:142-153), and a block whose norms
-sit on the branches' outputs."""
+"""Arrangements of a layer's parts: the pre-norm residual block (pyre/model.py:142-153), a block whose norms
+sit on the branches' outputs, and a block whose branches read one norm's output side by side."""
 
 from __future__ import annotations
 
@@ -106,3 +106,66 @@ class OutputNormBlock(Part):
 
 
 register_part("block", "output_norm", OutputNormBlock)
+
+
+class ParallelBlock(Part):
+    """x = x + m * (g1 * mixer(h) + g2 * ffn(h)) with h = norm1(x): ONE norm, both branches read its output, and
+    their results enter the stream together.  ``residual_mult`` is m; ``layer_scale``: g1 and g2 are gains per
+    feature read from the checkpoint (names ``ls1`` / ``ls2``), else ones.  ``ffn`` None: the layer has the mixer
+    only.
+
+    Nothing is added here: the branches travel as ``ops.ScaledSum`` (each with its gain times m, formed once in
+    fp32 at load) to the next norm, whose kernel adds them to the fp32 stream while it normalises."""
+
+    graph_safe = True
+
+    DEFAULT_NAMES = {"norm1": "norm1.", "mixer": "mixer.", "ffn": "ffn.", "ls1": "ls1", "ls2": "ls2"}
+
+    def __init__(self, dtype, device, width: int, norm1: PartSpec, mixer: PartSpec, ffn: "PartSpec | None" = None,
+                 residual_mult: float = 1.0, layer_scale: bool = False, names: "dict[str, str] | None" = None):
+        super().__init__(dtype, device)
+        self.names = dict(self.DEFAULT_NAMES, **(names or {}))
+        self.width, self.residual_mult, self.layer_scale = int(width), float(residual_mult), bool(layer_scale)
+        self.norm1 = make_part("norm", norm1, dtype, device)
+        self.mixer = make_part("mixer", mixer, dtype, device)
+        self.ffn = make_part("ffn", ffn, dtype, device) if ffn is not None else None
+        self.gain1 = self.gain2 = None
+
+    def children(self):
+        out = {self.names["norm1"]: self.norm1, self.names["mixer"]: self.mixer}
+        if self.ffn is not None:
+            out[self.names["ffn"]] = self.ffn
+        return out
+
+    def tensors(self):
+        from ..weights.specs import TensorSpec
+        if not self.layer_scale:
+            return {}
+        t = {self.names["ls1"]: TensorSpec((self.width,), role="vector", init=("normal", 1.0, 0.1))}
+        if self.ffn is not None:
+            t[self.names["ls2"]] = TensorSpec((self.width,), role="vector", init=("normal", 1.0, 0.1))
+        return t
+
+    def load(self, tensors):
+        import torch
+        m = self.residual_mult
+        ones = torch.ones(self.width, dtype=torch.float32, device=self.device) if not self.layer_scale else None
+        self.gain1 = (tensors[self.names["ls1"]] if self.layer_scale else ones) * m
+        if self.ffn is not None:
+            self.gain2 = (tensors[self.names["ls2"]] if self.layer_scale else ones) * m
+
+    def kernel_libraries(self):
+        return ["parallel_block"]
+
+    def forward(self, ctx, x, pending, call):
+        from ..kernels import ops
+        if pending is not None and isinstance(pending, ops.ScaledSum) and not getattr(self.norm1, "takes_scaled_sum", False):
+            pending = ops.materialize(pending)
+        h = self.norm1.forward(ctx, x, delta=pending)
+        terms = [(self.mixer.forward(ctx, h, call), self.gain1)]
+        if self.ffn is not None:
+            terms.append((self.ffn.forward(ctx, h), self.gain2))
+        return x, ops.ScaledSum(terms, self.dtype)
+
+
+register_part("block", "parallel", ParallelBlock)

@@ -10,14 +10,23 @@ from .base import Part, PartSpec, make_part, register_part
 
 
 class TokenEmbedding(Part):
-    """x[t] = table[token[t]], widened to the fp32 residual stream."""
+    """x[t] = table[token[t]], widened to the fp32 residual stream.  ``norm``: a norm part applied to the rows
+    right away (it must offer ``normalize_stream``); its tensors lie under ``norm_prefix`` after the table's name."""
 
     graph_safe = True
 
-    def __init__(self, dtype, device, vocab: int, width: int, tensor_name: str = "weight"):
+    def __init__(self, dtype, device, vocab: int, width: int, tensor_name: str = "weight", norm: "PartSpec | None" = None,
+                 norm_prefix: str = ".norm"):
         super().__init__(dtype, device)
         self.vocab, self.width, self.tensor_name = int(vocab), int(width), str(tensor_name)
         self.table = None
+        self.norm = make_part("norm", norm, dtype, device) if norm is not None else None
+        self.norm_prefix = str(norm_prefix)
+        if self.norm is not None and not hasattr(self.norm, "normalize_stream"):
+            raise ValueError(f"{type(self.norm).__name__} cannot follow the embedding: it has no normalize_stream")
+
+    def children(self):
+        return {self.tensor_name + self.norm_prefix: self.norm} if self.norm is not None else {}
 
     def tensors(self):
         return {self.tensor_name: TensorSpec((self.vocab, self.width))}
@@ -29,7 +38,8 @@ class TokenEmbedding(Part):
         return ["elementwise"]
 
     def forward(self, ctx):
-        return ops.embedding(self.table, ctx.token_ids, err_flag=ctx.error_flag)
+        x = ops.embedding(self.table, ctx.token_ids, err_flag=ctx.error_flag)
+        return x if self.norm is None else self.norm.normalize_stream(ctx, x)
 
 
 class LinearHead(Part):

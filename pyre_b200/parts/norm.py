@@ -1,6 +1,8 @@
-"""RMSNorm (pyre/model.py:22-38), fused with the residual add that precedes it."""
+"""RMSNorm (pyre/model.py:22-38) and a layer norm, each fused with the residual add that precedes it."""
 
 from __future__ import annotations
+
+import torch
 
 from ..kernels import ops
 from ..weights.specs import TensorSpec
@@ -45,3 +47,38 @@ class RMSNorm(Part):
 
 
 register_part("norm", "rms_norm", RMSNorm)
+
+
+class LayerNorm(Part):
+    """h = (v - mean(v)) / sqrt(var(v) + eps) * gain with v = x + delta, all in fp32, no bias; var is the mean
+    squared deviation.  ``x`` is the fp32 residual stream and receives the sum.  ``delta`` may be an
+    ``ops.ScaledSum`` (several branch outputs, each with a gain per feature): the kernel adds its terms itself.
+    ``tensor_name``: the local name of the weight ("" when the prefix is the whole name).
+    ``normalize_stream`` applies the norm to the stream itself (fp32 in, fp32 out): a norm right after the
+    embedding."""
+
+    graph_safe = True
+    takes_scaled_sum = True
+
+    def __init__(self, dtype, device, width: int, eps: float, tensor_name: str = "weight"):
+        super().__init__(dtype, device)
+        self.width, self.eps, self.tensor_name = int(width), float(eps), str(tensor_name)
+        self.weight = None
+
+    def tensors(self):
+        return {self.tensor_name: TensorSpec((self.width,), role="vector", init=("normal", 1.0, 0.1))}
+
+    def load(self, tensors):
+        self.weight = tensors[self.tensor_name]
+
+    def kernel_libraries(self):
+        return ["parallel_block"]
+
+    def forward(self, ctx, x, delta=None, rows=None, update_x=True, scaled_ok=False):
+        return ops.add_layernorm(x, delta, self.weight, self.eps, self.dtype, rows=rows, update_x=update_x)
+
+    def normalize_stream(self, ctx, x):
+        return ops.add_layernorm(x, None, self.weight, self.eps, torch.float32, act_dtype=self.dtype)
+
+
+register_part("norm", "layer_norm", LayerNorm)

@@ -11,7 +11,7 @@ from .base import HeadGeometry, PositionEncoding, register_part
 
 class Rotary(PositionEncoding):
     """inv_freq[j] = theta^(-2j / rotary_dim) for j < rotary_dim / 2, computed with the
-    reference's fp32 expression (pyre/model.py:45-47); per step, cos and sin of
+    reference's fp32 expression (pyre/model.py:45-47), or in 64-bit rounded once (``exact_frequencies``); per step, cos and sin of
     float(position) * inv_freq for the step's tokens, shared by all layers that have
     the same settings.  ``rotary_dim`` < head_dim rotates only the first dims of a head.  Bias, rotation of
     q and k and the paged write of k and v are one kernel (``ops.qkv_rope_write``)."""
@@ -24,8 +24,12 @@ class Rotary(PositionEncoding):
         self.head_dim = int(head_dim)
         self.rotary_dim = int(rotary_dim if rotary_dim is not None else head_dim)
         self.theta = float(theta)
-        if pairing != "half":
-            raise ops.UnsupportedSize(f"rotary pairing {pairing!r}: only the half-split pairing is implemented")
+        if pairing not in ("half", "interleaved"):
+            raise ops.UnsupportedSize(f"rotary pairing {pairing!r}: known are 'half' and 'interleaved'")
+        # "half" pairs dims (j, j + rotary_dim / 2), "interleaved" pairs neighbours (2j, 2j + 1); the angles are the
+        # same.  The fused q/k/v kernels of ``apply`` rotate half-split pairs only; a mixer with a kernel of its own
+        # takes the tables (``rotation``) and ``pairing``.
+        self.pairing = pairing
         if self.rotary_dim % 2 or self.rotary_dim > self.head_dim:
             raise ops.UnsupportedSize(f"rotary_dim {self.rotary_dim} must be even and <= head_dim")
         if exact_frequencies:
@@ -53,7 +57,14 @@ class Rotary(PositionEncoding):
         cos, sin = self.tables(ctx)
         return cos, sin, self.rotary_dim
 
+    def apply_layout(self, ctx, proj, layout, q_norm, k_norm, norm_eps, kv, cache_layer):
+        if self.pairing != "half":
+            raise ops.UnsupportedSize("the q/k/v kernels rotate half-split pairs only")
+        return super().apply_layout(ctx, proj, layout, q_norm, k_norm, norm_eps, kv, cache_layer)
+
     def apply(self, ctx, qkv, bias, heads: HeadGeometry, kv, cache_layer):
+        if self.pairing != "half":
+            raise ops.UnsupportedSize("the q/k/v kernels rotate half-split pairs only")
         if heads.head_dim != self.head_dim:
             raise ValueError(f"rotary part built for head_dim {self.head_dim}, used with {heads.head_dim}")
         cos, sin = self.tables(ctx)

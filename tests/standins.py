@@ -194,6 +194,140 @@ def feed_tokens(token_ids, dst, src, prev):
             token_ids[d] = prev[s]
 
 
+
+# --------------------------------------------------------------------------- layers whose branches share one norm
+def _branch(t):
+    from pyre_b200.kernels import ops
+    if isinstance(t, ops.PartialSums):
+        return t.parts.sum(0)
+    return t.float()
+
+
+def add_layernorm(x, delta, weight, eps, out_dtype, rows=None, update_x=True, act_dtype=None):
+    from pyre_b200.kernels import ops
+    v = x
+    if delta is not None:
+        terms = delta.terms if isinstance(delta, ops.ScaledSum) else [(delta, torch.ones_like(weight))]
+        add = sum(g * _branch(t) for t, g in terms)
+        v = x + add
+        if rows is None and update_x:
+            x.copy_(v)
+    if rows is not None:
+        v = v[rows.long()]
+    dev = v - v.mean(-1, keepdim=True)
+    return (dev * torch.rsqrt(dev.pow(2).mean(-1, keepdim=True) + eps) * weight).to(out_dtype)
+
+
+def act_mul(gate_up, kind):
+    g, u = gate_up.float().chunk(2, dim=1)
+    a = torch.nn.functional.silu(g) if kind == "silu" else torch.nn.functional.gelu(g, approximate="tanh")
+    return (a * u).to(gate_up.dtype)
+
+
+def _turn_pairs(v, cos, sin, rot):
+    """Neighbouring pairs of the first ``rot`` entries of the last axis turn by the token's angles; v [T, ..., n]."""
+    if not rot:
+        return v
+    shape = [v.shape[0]] + [1] * (v.dim() - 2) + [rot // 2]
+    c, s = cos.view(shape), sin.view(shape)
+    a, b = v[..., 0:rot:2], v[..., 1:rot:2]
+    out = v.clone()
+    out[..., 0:rot:2] = a * c - b * s
+    out[..., 1:rot:2] = b * c + a * s
+    return out
+
+
+def latent_prepare(proj, q_col, q_rank, c_col, rank, rope, rot, wq, wc, eps, cos, sin, cache_layer, slot_mapping, page_size,
+                   act_dtype):
+    x = _branch(proj)
+    T = x.shape[0]
+    rms = lambda v, w: v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * w
+    cq = rms(x[:, q_col:q_col + q_rank], wq).to(act_dtype) if q_rank else None
+    if cache_layer is not None:
+        c = rms(x[:, c_col:c_col + rank], wc)
+        r = _turn_pairs(x[:, c_col + rank:c_col + rank + rope], cos, sin, rot)
+        assert cache_layer.shape[1:3] == (1, 1)
+        for t in range(T):
+            page, off = divmod(int(slot_mapping[t]), page_size)
+            cache_layer[page, 0, 0, off, :] = 0
+            cache_layer[page, 0, 0, off, :rank + rope] = torch.cat([c[t], r[t]]).to(cache_layer.dtype)
+    return cq
+
+
+def latent_rotate_q(q, qa, cos, sin, n_heads, dq, rope, rot, rank):
+    T = q.shape[0]
+    tail = _turn_pairs(q.float().view(T, n_heads, dq + rope)[..., dq:], cos, sin, rot)
+    qa[..., rank:] = 0
+    qa[..., rank:rank + rope] = tail.to(qa.dtype)
+
+
+def latent_attention(ctx, qa, cache_layer, block_table, rank, rope, scale, window):
+    T, nh, row = qa.shape
+    page_size = cache_layer.shape[3]
+    out = torch.empty((T, nh, rank), dtype=qa.dtype)
+    for t in range(T):
+        b, p = int(ctx.seq_of_token[t]), int(ctx.positions[t])
+        lo = 0 if not window else max(0, p - window + 1)
+        pos = torch.arange(lo, p + 1)
+        pages = block_table[b].long()[pos // page_size]
+        assert (pages >= 0).all(), f"token {t}: a key in its window lies on a page that was given back"
+        rows = cache_layer[pages, 0, 0, pos % page_size, :].float()             # [keys, row]
+        scores = qa[t].float()[:, :rank + rope] @ rows[:, :rank + rope].t() * scale
+        out[t] = (torch.softmax(scores, dim=-1) @ rows[:, :rank]).to(qa.dtype)
+    return out
+
+
+def headwise_linear(x, w, out=None):
+    T, H, _ = x.shape
+    N, K = w.shape[1:]
+    y = torch.einsum("thk,hnk->thn", x.float()[..., :K], w.float()).to(x.dtype).contiguous()
+    if out is None:
+        return y
+    out[..., :N] = y
+    return out
+
+
+def route(h, w, correction, top, scale):
+    s = torch.softmax(h.float() @ w.t(), dim=-1)
+    choice = s if correction is None else s + correction
+    idx = choice.topk(top, dim=-1).indices
+    return idx.to(torch.int32), s.gather(-1, idx) * scale
+
+
+def group_pairs(idx, n_experts):
+    T, top = idx.shape
+    flat = idx.reshape(-1).long()
+    order = [p for e in range(n_experts) for p in range(T * top) if flat[p] == e]
+    counts = [int((flat == e).sum()) for e in range(n_experts)]
+    offsets = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32)
+    place_of = torch.full((T * top,), -1, dtype=torch.int32)
+    src = torch.zeros(T * top, dtype=torch.int32)
+    for place, p in enumerate(order):
+        place_of[p] = place
+        src[place] = p // top
+    return offsets, place_of.view(T, top), src
+
+
+def expert_linear(x, w, offsets, src, n_places, out_dtype=None):
+    E, N, K = w.shape
+    out = torch.full((n_places, N), float("nan"), dtype=out_dtype or x.dtype)      # places that no expert owns are never read
+    for e in range(E):
+        for p in range(int(offsets[e]), int(offsets[e + 1])):
+            r = int(src[p]) if src is not None else p
+            out[p] = (x[r].float() @ w[e].float().t()).to(out.dtype)
+    return out
+
+
+def combine_pairs(y, h, place_of, weight):
+    T, H = h.shape
+    out = torch.zeros((T, H), dtype=torch.float32)
+    for t in range(T):
+        for k in range(place_of.shape[1]):
+            p = int(place_of[t, k])
+            out[t] += weight[t, k] * (y[p] if p >= 0 else h[t].float())
+    return out
+
+
 def install(monkeypatch) -> None:
     """Put the stand-ins in place of the kernels for one test (float32 models on the CPU)."""
     from pyre_b200.engine import step
@@ -205,7 +339,10 @@ def install(monkeypatch) -> None:
                          qkv_rope_write=qkv_rope_write, paged_attention_generic=paged_attention_generic,
                          sgemm_nt=sgemm_nt, silu_mul=silu_mul, sample=sample, feed_tokens=feed_tokens, cast_rows=cast_rows,
                          norm_add=norm_add, activation=activation, linear_act=linear_act, qk_norm_rope_write=qk_norm_rope_write,
-                         sigmoid_gate=sigmoid_gate, rmsnorm_gate=rmsnorm_gate, linear_attention=linear_attention).items():
+                         sigmoid_gate=sigmoid_gate, rmsnorm_gate=rmsnorm_gate, linear_attention=linear_attention,
+                         add_layernorm=add_layernorm, act_mul=act_mul, latent_prepare=latent_prepare, latent_rotate_q=latent_rotate_q,
+                         latent_attention=latent_attention, headwise_linear=headwise_linear, route=route, group_pairs=group_pairs,
+                         expert_linear=expert_linear, combine_pairs=combine_pairs).items():
         monkeypatch.setattr(ops, name, fn)
     monkeypatch.setattr(ops, "device_error_flag", lambda device: flag)
     monkeypatch.setattr(ops, "check_device_errors", lambda device="cpu": None)
