@@ -273,3 +273,305 @@ PYRE_API int pyre_latent_attention_exact(const void* qa, const void* cache, void
     PYRE_LAUNCH_CHECK();
     return 0;
 }
+
+// ---------------------------------------------------------------------------
+// bfloat16 on the tensor cores (mma.sync m16n8k16, fp32 accumulators), for prompt portions and decoded tokens
+// alike.  All heads of a token read the same cached rows, so the heads are stacked on the MMA's rows: a CTA owns 64
+// rows = (token, head) pairs of one entry (`hg` heads per token, 64 / hg tokens), four warps of 16 rows.  The keys
+// of the tile's window travel through shared memory in tiles of 32 rows (cp.async, two buffers); a cached row is
+// the key (all `kd` entries, S = Q K^T) and, by its first `rank` entries, the value (O += P V, the B operand
+// fetched with ldmatrix.trans from the same tile).  Softmax online in fp32; P enters the second product as bf16.
+// A CTA holds the output columns [128 z, 128 z + 128) of its rows (blockIdx.z); latents wider than 128 recompute S
+// per 128 columns.  With `n_splits` > 1 the key tiles of a row tile are shared among that many CTAs, which leave
+// unnormalised partial outputs with their maxima and sums in scratch memory for the combining kernel.
+//   qa [T, nh, row] absorbed queries (zeros beyond kd); cache [page][page_size][row]; out [T, nh, rank]
+//   row % 16 == 0 (the padding of queries and cache rows is zero, so it adds nothing to a score)
+// ---------------------------------------------------------------------------
+constexpr int LM_ROWS = 64, LM_KT = 32, LM_DV = 128;
+
+__device__ __forceinline__ void lm_ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void lm_ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void lm_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t lm_pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(128) latent_attention_mma_kernel(
+    const __nv_bfloat16* qa, const __nv_bfloat16* cache, __nv_bfloat16* out, float* part_o, float* part_ml,
+    const int* block_table, int bt_stride, const int* cu_seqlens, const int* positions, int n_seqs, int nh, int hg, int rank,
+    int row, int page_size, int window, float scale_log2, int n_splits, int max_len, long long n_pages, int* err_flag) {
+    extern __shared__ __align__(16) unsigned char lm_smem[];
+    __shared__ int item[3];
+    pdl_trigger();
+    pdl_wait();
+    const int ld = row + 8;                                      // padded row of the shared tiles, in elements
+    __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(lm_smem);          // [64][ld]
+    __nv_bfloat16* k_s = q_s + LM_ROWS * ld;                                  // [2][32][ld]
+    const int tq = LM_ROWS / hg;                                 // tokens of a row tile
+    if (threadIdx.x == 0) {
+        int tile = blockIdx.x;
+        item[0] = -1;
+        for (int b = 0; b < n_seqs; ++b) {
+            const int n = cu_seqlens[b + 1] - cu_seqlens[b];
+            if (max_len > 0 && n > max_len) continue;            // entries that another kernel takes
+            const int tiles = (n + tq - 1) / tq;
+            if (tile < tiles) {
+                item[0] = b;
+                item[1] = cu_seqlens[b] + tile * tq;
+                item[2] = min(tq, n - tile * tq);
+                break;
+            }
+            tile -= tiles;
+        }
+    }
+    __syncthreads();
+    const int seq = item[0];
+    if (seq < 0) return;
+    const int tok0 = item[1], ntok = item[2];
+    const int h0 = blockIdx.y * hg, nhere = min(hg, nh - h0);
+    const int split = blockIdx.z % n_splits, chunk = blockIdx.z / n_splits;
+    const int c0 = chunk * LM_DV;                                // first output column of this CTA
+    const int p_first = positions[tok0];
+    const int k_hi = p_first + ntok - 1;
+    const int k_lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
+    const int k_al = (k_lo / LM_KT) * LM_KT;
+    const int tiles_total = (k_hi + 1 - k_al + LM_KT - 1) / LM_KT;
+    const int per = (tiles_total + n_splits - 1) / n_splits;
+    const int tile_lo = split * per, tile_hi = min(tiles_total, tile_lo + per);
+    const int* table = block_table + (size_t)seq * bt_stride;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int vecs = row / 8;                                    // 16-byte pieces of a row
+
+    // the queries of the tile's rows
+    for (int idx = threadIdx.x; idx < LM_ROWS * vecs; idx += blockDim.x) {
+        const int r = idx / vecs, v = idx - r * vecs;
+        const int tt = r / hg, hh = r - tt * hg;
+        uint4 val = make_uint4(0, 0, 0, 0);
+        if (tt < ntok && hh < nhere) val = *reinterpret_cast<const uint4*>(qa + ((size_t)(tok0 + tt) * nh + h0 + hh) * row + v * 8);
+        *reinterpret_cast<uint4*>(q_s + r * ld + v * 8) = val;
+    }
+    auto load_keys = [&](int buf, int tile) {
+        __nv_bfloat16* dst = k_s + (size_t)buf * LM_KT * ld;
+        const int pos0 = k_al + tile * LM_KT;
+        for (int idx = threadIdx.x; idx < LM_KT * vecs; idx += blockDim.x) {
+            const int j = idx / vecs, v = idx - j * vecs;
+            const int pos = pos0 + j;
+            __nv_bfloat16* d = dst + j * ld + v * 8;
+            if (pos >= k_lo && pos <= k_hi) {
+                const int page = pyre_checked_page(table[pos / page_size], n_pages, err_flag);
+                const __nv_bfloat16* src = cache + ((size_t)page * page_size + pos % page_size) * row + v * 8;
+                const uint32_t daddr = (uint32_t)__cvta_generic_to_shared(d);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(daddr), "l"(src));
+            } else {
+                *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::);
+    };
+
+    // this thread's two rows: g and g + 8 of the warp's 16
+    int p_row[2], lo_row[2];
+    bool live[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const int r = warp * 16 + (lane >> 2) + u * 8;
+        const int tt = r / hg, hh = r - tt * hg;
+        live[u] = tt < ntok && hh < nhere;
+        p_row[u] = p_first + tt;
+        lo_row[u] = (window > 0 && p_row[u] - window + 1 > 0) ? p_row[u] - window + 1 : 0;
+    }
+    float o[LM_DV / 8][4];
+#pragma unroll
+    for (int i = 0; i < LM_DV / 8; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[i][e] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    const int nt_live = min(LM_DV, ((rank - c0 + 7) / 8) * 8) / 8;      // 8-column tiles of the output that exist here
+
+    if (tile_lo < tile_hi) load_keys(0, tile_lo);
+    for (int tile = tile_lo; tile < tile_hi; ++tile) {
+        const int buf = (tile - tile_lo) & 1;
+        if (tile + 1 < tile_hi) {
+            load_keys(buf ^ 1, tile + 1);
+            asm volatile("cp.async.wait_group 1;" ::);
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::);
+        }
+        __syncthreads();
+        const __nv_bfloat16* kt = k_s + (size_t)buf * LM_KT * ld;
+        float s[LM_KT / 8][4];
+#pragma unroll
+        for (int i = 0; i < LM_KT / 8; ++i)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[i][e] = 0.f;
+        for (int kk = 0; kk < row; kk += 16) {
+            uint32_t a[4], b[LM_KT / 16][4];
+            lm_ldmatrix_x4(a, q_s + (warp * 16 + (lane & 15)) * ld + kk + (lane >> 4) * 8);
+#pragma unroll
+            for (int j = 0; j < LM_KT / 16; ++j)
+                lm_ldmatrix_x4(b[j], kt + (j * 16 + (lane & 7) + ((lane >> 4) << 3)) * ld + kk + ((lane >> 3) & 1) * 8);
+#pragma unroll
+            for (int i = 0; i < LM_KT / 8; ++i) lm_mma(s[i], a, b[i >> 1][(i & 1) * 2], b[i >> 1][(i & 1) * 2 + 1]);
+        }
+        // mask, and the tile's row maxima
+        const int pos0 = k_al + tile * LM_KT;
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int i = 0; i < LM_KT / 8; ++i)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int u = e >> 1;
+                const int pos = pos0 + i * 8 + (lane & 3) * 2 + (e & 1);
+                const bool ok = live[u] && pos >= lo_row[u] && pos <= p_row[u];
+                s[i][e] = ok ? s[i][e] * scale_log2 : -INFINITY;
+                mx[u] = fmaxf(mx[u], s[i][e]);
+            }
+        float alpha[2], base[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            mx[u] = fmaxf(mx[u], __shfl_xor_sync(0xffffffffu, mx[u], 1));
+            mx[u] = fmaxf(mx[u], __shfl_xor_sync(0xffffffffu, mx[u], 2));
+            const float m_new = fmaxf(m[u], mx[u]);
+            base[u] = m_new == -INFINITY ? 0.f : m_new;          // a row without a key so far: every term is zero
+            alpha[u] = exp2f(m[u] - base[u]);
+            m[u] = m_new;
+        }
+        float sum[2] = {0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < LM_KT / 8; ++i)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float p = exp2f(s[i][e] - base[e >> 1]);
+                s[i][e] = p;
+                sum[e >> 1] += p;
+            }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            sum[u] += __shfl_xor_sync(0xffffffffu, sum[u], 1);
+            sum[u] += __shfl_xor_sync(0xffffffffu, sum[u], 2);
+            l[u] = l[u] * alpha[u] + sum[u];
+        }
+#pragma unroll
+        for (int i = 0; i < LM_DV / 8; ++i) {
+            o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+            o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+        }
+        // O += P V: the tile's rows again, their entries c0 .. as values
+#pragma unroll
+        for (int kk = 0; kk < LM_KT / 16; ++kk) {
+            uint32_t a[4];
+            a[0] = lm_pack(s[2 * kk][0], s[2 * kk][1]);
+            a[1] = lm_pack(s[2 * kk][2], s[2 * kk][3]);
+            a[2] = lm_pack(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+            a[3] = lm_pack(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+            for (int i = 0; i < LM_DV / 8; i += 2) {
+                if (i < nt_live) {
+                    uint32_t b[4];
+                    lm_ldmatrix_x4_trans(b, kt + (kk * 16 + (lane & 15)) * ld + c0 + i * 8 + (lane >> 4) * 8);
+                    lm_mma(o[i], a, b[0], b[1]);
+                    lm_mma(o[i + 1], a, b[2], b[3]);
+                }
+            }
+        }
+        __syncthreads();      // the buffer is loaded again two tiles on
+    }
+
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        if (!live[u]) continue;
+        const int r = warp * 16 + (lane >> 2) + u * 8;
+        const int tt = r / hg, hh = r - tt * hg;
+        const size_t th = (size_t)(tok0 + tt) * nh + h0 + hh;
+        if (n_splits == 1) {
+            const float inv = 1.0f / l[u];
+#pragma unroll
+            for (int i = 0; i < LM_DV / 8; ++i)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int c = c0 + i * 8 + (lane & 3) * 2 + e;
+                    if (c < rank) out[th * rank + c] = __float2bfloat16_rn(o[i][u * 2 + e] * inv);
+                }
+        } else {
+            float* po = part_o + (th * n_splits + split) * rank;
+#pragma unroll
+            for (int i = 0; i < LM_DV / 8; ++i)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int c = c0 + i * 8 + (lane & 3) * 2 + e;
+                    if (c < rank) po[c] = o[i][u * 2 + e];
+                }
+            if (chunk == 0 && (lane & 3) == 0) {
+                part_ml[(th * n_splits + split) * 2] = m[u];
+                part_ml[(th * n_splits + split) * 2 + 1] = l[u];
+            }
+        }
+    }
+}
+
+// out[t, h] = sum_s O_s 2^(m_s - m) / sum_s l_s 2^(m_s - m): the shares of one (token, head); maxima are base-2 exponents
+__global__ void latent_combine_kernel(const float* part_o, const float* part_ml, __nv_bfloat16* out, int n_splits, int rank) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t th = blockIdx.x;
+    const float* ml = part_ml + th * n_splits * 2;
+    float mx = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) mx = fmaxf(mx, ml[2 * s]);
+    float denom = 0.f;
+    for (int s = 0; s < n_splits; ++s) denom += ml[2 * s] == -INFINITY ? 0.f : ml[2 * s + 1] * exp2f(ml[2 * s] - mx);
+    const float inv = 1.0f / denom;
+    for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < n_splits; ++s)
+            if (ml[2 * s] != -INFINITY) acc = fmaf(part_o[(th * n_splits + s) * rank + c], exp2f(ml[2 * s] - mx), acc);
+        out[th * rank + c] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
+// n_tiles: an upper bound of the row tiles over the entries this launch takes (sum of ceil(len / (64 / hg)));
+// max_len > 0: only entries of at most that many tokens.  part_o [T, nh, n_splits, rank], part_ml [T, nh, n_splits, 2].
+PYRE_API int pyre_latent_attention_mma(const void* qa, const void* cache, void* out, float* part_o, float* part_ml,
+                                       const int* block_table, int bt_stride, const int* cu_seqlens, const int* positions,
+                                       int n_tokens, int n_seqs, int n_tiles, int nh, int rank, int row, int page_size, int window,
+                                       float scale, int n_splits, int max_len, long long n_pages, int* err_flag,
+                                       cudaStream_t stream) {
+    if (n_tokens <= 0 || n_tiles <= 0) return 0;
+    if (rank <= 0 || row < rank || row % 16 || nh <= 0 || page_size <= 0 || n_splits < 1) return PYRE_ERR_BAD_ARG;
+    if (n_splits > 1 && (!part_o || !part_ml)) return PYRE_ERR_BAD_ARG;
+    const int hg = min(nh, LM_ROWS);
+    const size_t smem = (size_t)(LM_ROWS + 2 * LM_KT) * (row + 8) * sizeof(__nv_bfloat16);
+    if (smem > 200 * 1024) return PYRE_ERR_UNSUPPORTED;
+    static bool attr_set[PYRE_MAX_DEVICES] = {};
+    const int dev = pyre_current_device();
+    if (!attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(latent_attention_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return (int)e;
+        attr_set[dev] = true;
+    }
+    const int chunks = ceil_div(rank, LM_DV);
+    const float scale_log2 = scale * 1.4426950408889634f;
+    pyre_launch(latent_attention_mma_kernel, dim3(n_tiles, ceil_div(nh, hg), chunks * n_splits), dim3(128), smem, stream,
+                (const __nv_bfloat16*)qa, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, part_o, part_ml, block_table, bt_stride,
+                cu_seqlens, positions, n_seqs, nh, hg, rank, row, page_size, window, scale_log2, n_splits, max_len, n_pages,
+                err_flag);
+    PYRE_LAUNCH_CHECK();
+    if (n_splits > 1) {
+        pyre_launch(latent_combine_kernel, dim3(n_tokens * nh), dim3(128), 0, stream, (const float*)part_o, (const float*)part_ml,
+                    (__nv_bfloat16*)out, n_splits, rank);
+        PYRE_LAUNCH_CHECK();
+    }
+    return 0;
+}

@@ -57,6 +57,7 @@ SIGNATURES: dict[str, tuple[str, list]] = {
     "pyre_latent_prepare": ("latent_attention", [P, P, I, LL, I, I, I, I, I, I, I, P, P, F, P, P, P, P, P, I, I, LL, I, I, P, P]),
     "pyre_latent_rotate_q": ("latent_attention", [P, P, P, P, I, I, I, I, I, I, I, I, P]),
     "pyre_latent_attention_exact": ("latent_attention", [P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, LL, P, P]),
+    "pyre_latent_attention_mma": ("latent_attention", [P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, F, I, I, LL, P, P]),
     "pyre_grouped_linear": ("grouped", [P, LL, LL, P, LL, P, LL, LL, P, P, P, I, I, I, I, I, I, I, I, P]),
     "pyre_route": ("grouped", [P, P, P, P, P, I, I, I, I, F, I, P]),
     "pyre_group_pairs": ("grouped", [P, I, I, I, P, P, P, P]),
@@ -84,7 +85,7 @@ DEFAULT_CLASS = {
     "pyre_sigmoid_gate": "gate", "pyre_rmsnorm_gate": "gate", "pyre_linear_attention_scan": "linear_attention",
     "pyre_linear_attention_chunked": "linear_attention",
     "pyre_add_layernorm": "norm", "pyre_scaled_sum": "norm", "pyre_act_mul": "activation", "pyre_latent_prepare": "rotary+write",
-    "pyre_latent_rotate_q": "rotary+write", "pyre_latent_attention_exact": "attention", "pyre_grouped_linear": "grouped_product",
+    "pyre_latent_rotate_q": "rotary+write", "pyre_latent_attention_exact": "attention", "pyre_latent_attention_mma": "attention", "pyre_grouped_linear": "grouped_product",
     "pyre_route": "router", "pyre_group_pairs": "router", "pyre_combine_pairs": "router",
 }
 

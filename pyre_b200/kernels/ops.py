@@ -1340,7 +1340,9 @@ class ScaledSum:
         T, H = self.shape
         args, stride = self._args(self.dtype)
         out = torch.empty((T, H), dtype=self.dtype, device=self.terms[0][1].device)
-        lib.call("pyre_scaled_sum", *args, stride, out.data_ptr(), T, H, _dt(self.dtype), _stream())
+        a = args
+        lib.call("pyre_scaled_sum", a[0], a[1], a[2], a[3], a[4], a[5], a[6], a[7], stride, out.data_ptr(), T, H, _dt(self.dtype),
+                 _stream())
         return out
 
 
@@ -1372,7 +1374,8 @@ def add_layernorm(x: torch.Tensor, delta: "ScaledSum | torch.Tensor | PartialSum
         _check(rows, "rows", torch.int32, 1)
         n_rows, update_x = rows.shape[0], False
     out = torch.empty((n_rows, H), dtype=out_dtype, device=x.device)
-    lib.call("pyre_add_layernorm", x.data_ptr(), *args, stride, weight.data_ptr(), out.data_ptr(),
+    a = args
+    lib.call("pyre_add_layernorm", x.data_ptr(), a[0], a[1], a[2], a[3], a[4], a[5], a[6], a[7], stride, weight.data_ptr(), out.data_ptr(),
              int(out_dtype == torch.float32 and act != torch.float32), _ptr(rows), n_rows, H, float(eps),
              int(bool(update_x and delta is not None)), _dt(act), _stream())
     return out
@@ -1592,7 +1595,67 @@ def combine_pairs(y: torch.Tensor, h: torch.Tensor, place_of: torch.Tensor, weig
     return out
 
 
+LATENT_MMA_ROWS = 64          # (token, head) rows of a CTA of the tensor-core kernel
+LATENT_MMA_KEYS = 32          # cached rows per key tile
+LATENT_MMA_COLS = 128         # output columns per CTA
+USE_LATENT_MMA = True
+
+
+def latent_mma_ok(dtype: torch.dtype, row: int) -> bool:
+    """The sizes the tensor-core latent attention takes (as its launcher checks them)."""
+    return USE_LATENT_MMA and dtype == torch.bfloat16 and row % 16 == 0 and (LATENT_MMA_ROWS + 2 * LATENT_MMA_KEYS) * (row + 8) * 2 <= 200 * 1024
+
+
+def latent_attention_splits(n_tiles: int, n_heads: int, rank: int, span: int) -> int:
+    """Into how many shares the tensor-core latent attention cuts the keys of every row tile: enough CTAs for about
+    one and a half per SM, at least four key tiles per share, at most 16.  ``span``: the most keys a tile walks."""
+    ctas = max(1, n_tiles * -(-n_heads // LATENT_MMA_ROWS) * -(-rank // LATENT_MMA_COLS))
+    tiles = -(-span // LATENT_MMA_KEYS) + 1
+    return int(max(1, min(int(1.5 * sm_count() / ctas), tiles // 4, 16)))
+
+
+def latent_attention_mma(qa: torch.Tensor, cache_layer: torch.Tensor, block_table: torch.Tensor, cu_seqlens: torch.Tensor,
+                         positions: torch.Tensor, n_tiles: int, rank: int, scale: float, window: "int | None", n_splits: int = 1,
+                         max_len: int = 0, out: "torch.Tensor | None" = None) -> torch.Tensor:
+    """bfloat16 attention of absorbed queries ``qa`` [T, nh, row] over latent rows on the tensor cores; ``n_tiles``:
+    an upper bound of the row tiles (64 // min(nh, 64) tokens each) of the entries taken (``max_len`` > 0: those of
+    at most that many tokens).  Returns [T, nh, rank]."""
+    _check(qa, "qa", torch.bfloat16, 3)
+    _check(cache_layer, "cache_layer", torch.bfloat16, 5)
+    _check(block_table, "block_table", torch.int32, 2)
+    _check(cu_seqlens, "cu_seqlens", torch.int32, 1)
+    _check(positions, "positions", torch.int32, 1)
+    T, nh, row = qa.shape
+    page_size = cache_layer.shape[3]
+    if tuple(cache_layer.shape[1:]) != (1, 1, page_size, row) or row < rank or not latent_mma_ok(qa.dtype, row):
+        raise UnsupportedSize(f"latent rows of {row} entries in {tuple(cache_layer.shape)}: the tensor-core kernel takes multiples of 16")
+    n_seqs = cu_seqlens.shape[0] - 1
+    if positions.shape[0] != T or block_table.shape[0] < n_seqs:
+        raise ValueError("cu_seqlens, positions and block_table do not match the batch")
+    if out is None:
+        out = torch.empty((T, nh, rank), dtype=qa.dtype, device=qa.device)
+    n_splits = int(n_splits)
+    part_o = part_ml = None
+    if n_splits > 1:
+        part_o = torch.empty((T, nh, n_splits, rank), dtype=torch.float32, device=qa.device)
+        part_ml = torch.empty((T, nh, n_splits, 2), dtype=torch.float32, device=qa.device)
+    lib.call("pyre_latent_attention_mma", qa.data_ptr(), cache_layer.data_ptr(), out.data_ptr(), _ptr(part_o), _ptr(part_ml),
+             block_table.data_ptr(), block_table.stride(0), cu_seqlens.data_ptr(), positions.data_ptr(), T, n_seqs, int(n_tiles), nh,
+             int(rank), row, page_size, int(window or 0), float(scale), n_splits, int(max_len), cache_layer.shape[0],
+             device_error_flag(qa.device).data_ptr(), _stream())
+    return out
+
+
 def latent_attention(ctx, qa: torch.Tensor, cache_layer: torch.Tensor, block_table: torch.Tensor, rank: int, rope: int,
                      scale: float, window: "int | None") -> torch.Tensor:
-    """Attention of a whole step's absorbed queries over their sequences' latent rows; [T, nh, rank]."""
-    return latent_attention_exact(qa, cache_layer, block_table, ctx.seq_of_token, ctx.positions, rank, rope, scale, window)
+    """Attention of a whole step's absorbed queries over their sequences' latent rows; [T, nh, rank].  bfloat16 with
+    rows of a multiple of 16 entries: the tensor-core kernel; everything else: the exact one."""
+    T, nh, row = qa.shape
+    if not latent_mma_ok(qa.dtype, row):
+        return latent_attention_exact(qa, cache_layer, block_table, ctx.seq_of_token, ctx.positions, rank, rope, scale, window)
+    tq = LATENT_MMA_ROWS // min(nh, LATENT_MMA_ROWS)
+    lens = ctx.cu_seqlens_host[1:] - ctx.cu_seqlens_host[:-1]
+    n_tiles = int((-(-lens // tq)).sum())
+    span = ctx.max_context if not window else min(ctx.max_context, window + tq)
+    return latent_attention_mma(qa, cache_layer, block_table, ctx.cu_seqlens, ctx.positions, n_tiles, rank, scale, window,
+                                latent_attention_splits(n_tiles, nh, rank, span))

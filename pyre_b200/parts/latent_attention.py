@@ -48,8 +48,8 @@ class LatentAttention(Part):
             raise ValueError("the sizes of a latent attention are positive")
         if self.kv_rank > ops.LATENT_MAX_RANK:
             raise ops.UnsupportedSize(f"kv_rank {kv_rank}: the latent attention kernels take up to {ops.LATENT_MAX_RANK}")
-        # a cache row: latent, rotated key part, zeros up to a multiple of 8 entries (16-byte rows in bfloat16)
-        self.row = -(-(self.kv_rank + self.rope_dim) // 8) * 8
+        # a cache row: latent, rotated key part, zeros up to a multiple of 16 entries (whole k-steps of the MMA)
+        self.row = -(-(self.kv_rank + self.rope_dim) // 16) * 16
         self.position = make_part("position", position, dtype, device)
         if getattr(self.position, "pairing", "interleaved") != "interleaved":
             raise ops.UnsupportedSize("the latent attention kernels rotate neighbouring pairs")
@@ -90,6 +90,14 @@ class LatentAttention(Part):
 
     def state_spec(self):
         return None
+
+    def launch_key(self, n_rows, max_context):
+        # the tensor-core kernel's split count is chosen on the host from these numbers
+        if not ops.latent_mma_ok(self.dtype, self.row):
+            return ()
+        tq = ops.LATENT_MMA_ROWS // min(self.n_heads, ops.LATENT_MMA_ROWS)
+        span = max_context if not self.window else min(max_context, self.window + tq)
+        return (ops.latent_attention_splits(n_rows, self.n_heads, self.kv_rank, span),)
 
     def forward(self, ctx, h, call):
         kv = ctx.kv_group(call.kv_group)

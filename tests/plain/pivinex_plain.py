@@ -3,7 +3,9 @@ design's equations and sharing no code with the package.  A whole sequence at a 
 keys and values are recomputed from the layer's input.
 
 Weights are a dict name -> torch tensor (any dtype; widened here), the configuration is the dict that
-``config.json`` holds.
+``config.json`` holds.  ``lowp=True`` rounds to bfloat16 where an engine's bfloat16 path may (operands and results
+of matrix products, the cached latent and key part, the queries, the heads' outputs, activations); norms, angles,
+scores, the softmax, the router and the stream stay exact.  It measures what rounding alone costs.
 """
 
 from __future__ import annotations
@@ -13,6 +15,15 @@ import math
 import torch
 
 F64 = torch.float64
+
+
+def _r(x, lowp):
+    return x.to(torch.bfloat16).to(F64) if lowp else x
+
+
+def matmul(x, w, lowp=False):
+    """x W^T for a weight stored [out, in]."""
+    return _r(_r(x, lowp) @ w.to(F64).T, lowp)
 
 
 def layer_norm(x, gain, eps):
@@ -52,7 +63,7 @@ def rotate_pairs(v, positions, base, dims):
     return out
 
 
-def latent_attention(h, w, prefix, mixer, eps):
+def latent_attention(h, w, prefix, mixer, eps, lowp=False):
     """Softmax attention whose keys and values are expanded per head from one low-rank latent per token and one
     rotated key part shared by the heads.  ``h`` [T, width] is one sequence from position 0; returns [T, width]."""
     T = h.shape[0]
@@ -60,14 +71,14 @@ def latent_attention(h, w, prefix, mixer, eps):
     rank = mixer["kv_rank"]
     g = lambda n: w[prefix + n].to(F64)
     pos = torch.arange(T)
-    cq = rms_norm(h @ g("dq").T, g("dq.norm"), eps)
-    q = (cq @ g("uq").T).view(T, H, dn + dr)
-    q_plain, q_rot = q[..., :dn], rotate_pairs(q[..., dn:], pos, mixer["rot"]["base"], mixer["rot"]["dims"])
-    down = h @ g("dkv").T
-    c = rms_norm(down[:, :rank], g("dkv.norm"), eps)
-    k_rot = rotate_pairs(down[:, rank:], pos, mixer["rot"]["base"], mixer["rot"]["dims"])       # [T, dr], all heads
-    k_plain = (c @ g("uk").T).view(T, H, dn)
-    val = (c @ g("uv").T).view(T, H, dv)
+    cq = _r(rms_norm(matmul(h, g("dq"), lowp), g("dq.norm"), eps), lowp)
+    q = matmul(cq, g("uq"), lowp).view(T, H, dn + dr)
+    q_plain, q_rot = q[..., :dn], _r(rotate_pairs(q[..., dn:], pos, mixer["rot"]["base"], mixer["rot"]["dims"]), lowp)
+    down = matmul(h, g("dkv"), lowp)
+    c = _r(rms_norm(down[:, :rank], g("dkv.norm"), eps), lowp)
+    k_rot = _r(rotate_pairs(down[:, rank:], pos, mixer["rot"]["base"], mixer["rot"]["dims"]), lowp)       # [T, dr], all heads
+    k_plain = matmul(c, g("uk"), lowp).view(T, H, dn)
+    val = matmul(c, g("uv"), lowp).view(T, H, dv)
     scores = (torch.einsum("ihd,jhd->hij", q_plain, k_plain) + torch.einsum("ihd,jd->hij", q_rot, k_rot)) * mixer["scale"]
     i, j = pos.view(-1, 1), pos.view(1, -1)
     seen = (j <= i)
@@ -76,28 +87,33 @@ def latent_attention(h, w, prefix, mixer, eps):
         seen = seen & (i - j < size)
     scores = scores.masked_fill(~seen, float("-inf"))
     p = torch.softmax(scores, dim=-1)
-    heads = torch.einsum("hij,jhd->ihd", p, val).reshape(T, H * dv)
-    return heads @ g("o").T
+    heads = _r(torch.einsum("hij,jhd->ihd", p, val).reshape(T, H * dv), lowp)
+    return matmul(heads, g("o"), lowp)
 
 
-def dense_ffn(h, w, prefix):
+def dense_ffn(h, w, prefix, lowp=False):
     g = lambda n: w[prefix + n].to(F64)
-    return (gelu_tanh(h @ g("gate").T) * (h @ g("up").T)) @ g("down").T
+    return matmul(_r(gelu_tanh(matmul(h, g("gate"), lowp)) * matmul(h, g("up"), lowp), lowp), g("down"), lowp)
 
 
-def route(h, w, prefix, router):
+def route(h, w, prefix, router, margins=None):
     """Per token the chosen experts and their weights: scores are a softmax over all router outputs; the choice
-    adds a correction per expert to the scores, the weights are the plain scores times a constant."""
+    adds a correction per expert to the scores, the weights are the plain scores times a constant.  ``margins``
+    receives, per token, by how much the last chosen output beat the best one left out."""
     z = h @ w[prefix + "router"].to(F64).T
     s = torch.softmax(z, dim=-1)
-    pick = (s + w[prefix + "correction"].to(F64)).topk(router["top"], dim=-1).indices
+    choice = s + w[prefix + "correction"].to(F64)
+    pick = choice.topk(router["top"], dim=-1).indices
+    if margins is not None and router["top"] < choice.shape[-1]:
+        ranked = choice.sort(dim=-1, descending=True).values
+        margins.extend((ranked[..., router["top"] - 1] - ranked[..., router["top"]]).reshape(-1).tolist())
     return pick, s.gather(-1, pick) * router["scale"]
 
 
-def moe_ffn(h, w, prefix, mlp):
+def moe_ffn(h, w, prefix, mlp, lowp=False, margins=None):
     router = mlp["router"]
     n_real = router["experts"]
-    pick, weight = route(h, w, prefix, router)
+    pick, weight = route(h, w, prefix, router, margins)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, a in zip(pick[t].tolist(), weight[t]):
@@ -105,21 +121,21 @@ def moe_ffn(h, w, prefix, mlp):
                 out[t] += a * h[t]
                 continue
             g = lambda n: w[f"{prefix}e{e}.{n}"].to(F64)
-            out[t] += a * ((silu(h[t] @ g("gate").T) * (h[t] @ g("up").T)) @ g("down").T)
+            out[t] += a * matmul(_r(silu(matmul(h[t], g("gate"), lowp)) * matmul(h[t], g("up"), lowp), lowp), g("down"), lowp)
     return out
 
 
-def layer(x, w, i, cfg):
+def layer(x, w, i, cfg, lowp=False, margins=None):
     L = cfg["layers"][i]
     eps = cfg["norm"]["eps"]
     pre = f"l{i}."
-    h = layer_norm(x, w[pre + "norm1"].to(F64), eps)
+    h = _r(layer_norm(x, w[pre + "norm1"].to(F64), eps), lowp)
     if L["type"] != "latent_attention":
         raise ValueError(L["type"])
-    branch = latent_attention(h, w, pre + "mix.", L["mixer"], eps) * w[pre + "ls1"].to(F64)
+    branch = latent_attention(h, w, pre + "mix.", L["mixer"], eps, lowp) * w[pre + "ls1"].to(F64)
     mlp = L.get("mlp")
     if mlp:
-        f = dense_ffn(h, w, pre + "mlp.") if mlp["kind"] == "dense" else moe_ffn(h, w, pre + "mlp.", mlp)
+        f = dense_ffn(h, w, pre + "mlp.", lowp) if mlp["kind"] == "dense" else moe_ffn(h, w, pre + "mlp.", mlp, lowp, margins)
         branch = branch + f * w[pre + "ls2"].to(F64)
     return x + cfg["residual_mult"] * branch
 
@@ -136,16 +152,16 @@ def layer_order(cfg):
     return order
 
 
-def forward(tokens, w, cfg, streams=None):
+def forward(tokens, w, cfg, streams=None, lowp=False, margins=None):
     """Logits [T, vocab] (float64) of one sequence; ``streams``: a list that receives the stream after every
-    layer run."""
+    layer run; ``margins``: a list that receives every router decision's margin."""
     eps = cfg["norm"]["eps"]
     e = layer_norm(w["embed"].to(F64)[torch.as_tensor(tokens)], w["embed.norm"].to(F64), eps)
     x = e
     for i, again in layer_order(cfg):
         if again:
             x = x + e
-        x = layer(x, w, i, cfg)
+        x = layer(x, w, i, cfg, lowp, margins)
         if streams is not None:
             streams.append(x)
-    return layer_norm(x, w["final.norm"].to(F64), eps) @ w["head"].to(F64).T
+    return _r(layer_norm(x, w["final.norm"].to(F64), eps), lowp) @ w["head"].to(F64).T
