@@ -649,6 +649,134 @@ def run_modovik(args) -> dict:
     return out
 
 
+def run_pivinex(args) -> dict:
+    """``--workload pivinex``: the Pivinex design (latent attention, a gated gelu and a routed feed-forward, random
+    weights) at two sets of layer sizes beside the Qwen2.5 decoder at equal width, heads and feed-forward size and as
+    many layers: a 2,048-token prompt step and decode steps at batch 8 and 64 with 2,048 tokens of context,
+    device-timed, and per kernel class the device time of one such step with the fraction of the measured peak
+    (copy bandwidth, or the cuBLAS figure where the flops bind).  Two layers: a dense and a routed feed-forward."""
+    import numpy as np
+    import torch
+
+    from pyre_b200 import Engine
+    from pyre_b200.config import config_from_dict
+    from pyre_b200.engine.step import StepEntry
+
+    peaks = load_peaks()
+    V = 32768
+    sizes = {
+        # width, heads, dim, rot, vdim, q_rank, kv_rank, window, dense ff, experts, identity, top, expert ff
+        "2k": dict(H=2048, nh=16, dn=128, dr=64, dv=128, qr=768, kr=256, win=1024, I=8192, E=32, ident=2, top=4, ff=1024),
+        "3.5k": dict(H=3584, nh=28, dn=128, dr=64, dv=128, qr=1536, kr=512, win=4096, I=18944, E=64, ident=0, top=6, ff=1408),
+    }
+    T, ctx_len, reps = PROMPT_LEN, 2048, max(3, args.prefill_reps)
+    rng = np.random.default_rng(0)
+    out = {"workload": "pivinex", "layers": 2, "peaks": peaks, "prompt": T, "decode_context": ctx_len, "sizes": {}}
+    for tag, z in sizes.items():
+        H, nh, dn, dr, dv, qr, kr, win, I, E, ident, top, ff = (z[k] for k in ("H", "nh", "dn", "dr", "dv", "qr", "kr", "win", "I", "E", "ident", "top", "ff"))
+        mixer = {"heads": nh, "dim": dn, "rot_dim": dr, "vdim": dv, "q_rank": qr, "kv_rank": kr, "scale": (dn + dr) ** -0.5,
+                 "mask": {"size": win}, "rot": {"dims": dr, "base": 1e6}}
+        raw_p = {"architecture": "Pivinex", "vocab": V, "width": H, "norm": {"eps": 1e-6}, "residual_mult": 0.5, "layers": [
+            {"type": "latent_attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": I}},
+            {"type": "latent_attention", "mixer": mixer, "mlp": {"kind": "moe", "expert": {"ff": ff},
+                                                                "router": {"experts": E, "identity": ident, "top": top, "scale": 1.0}}}]}
+        L = 2
+        raw_q = dict(CONFIG_7B, hidden_size=H, intermediate_size=I, num_attention_heads=nh, num_key_value_heads=4, head_dim=128,
+                     num_hidden_layers=L, vocab_size=V)
+        row = -(-(kr + dr) // 16) * 16
+
+        def work_pivinex(Tn, B, before):
+            """bytes and flops per class of one step of the two layers"""
+            per = Tn // B
+            first = np.arange(before, before + per)                      # positions of an entry's tokens
+            keys = B * float(np.minimum(first + 1, win).sum())           # query-key pairs inside the window
+            cached = B * min(before + per, win + per)                    # cached rows that are read
+            pairs = Tn * top                                             # (token, expert) pairs, all with weights at most
+            used = min(E, pairs)                                         # experts whose weights are read
+            down_cols = qr + kr + dr
+            return {
+                "qkv": {"bytes": L * (down_cols * H * 2 + Tn * (H + down_cols) * 2), "flops": 2.0 * L * Tn * H * down_cols},
+                "q_up": {"bytes": L * (nh * (dn + dr) * qr * 2 + Tn * (qr + nh * (dn + dr)) * 2), "flops": 2.0 * L * Tn * qr * nh * (dn + dr)},
+                "absorb": {"bytes": L * (nh * dn * kr * 2 + Tn * nh * (dn + kr) * 2), "flops": 2.0 * L * Tn * nh * dn * kr},
+                "attention": {"bytes": L * (cached * row * 2 + Tn * nh * (row + kr) * 2), "flops": 2.0 * L * nh * (kr + dr + kr) * keys},
+                "v_up": {"bytes": L * (nh * dv * kr * 2 + Tn * nh * (kr + dv) * 2), "flops": 2.0 * L * Tn * nh * kr * dv},
+                "o": {"bytes": L * (H * nh * dv * 2 + Tn * (nh * dv + H) * 2), "flops": 2.0 * L * Tn * nh * dv * H},
+                "gate_up": {"bytes": 2 * I * H * 2 + Tn * (H + 2 * I) * 2 + Tn * 3 * I * 2, "flops": 4.0 * Tn * H * I},
+                "down": {"bytes": H * I * 2 + Tn * (I + H) * 2, "flops": 2.0 * Tn * H * I},
+                "experts_gate_up": {"bytes": used * 2 * ff * H * 2 + pairs * (H + 2 * ff) * 2, "flops": 4.0 * pairs * H * ff},
+                "experts_down": {"bytes": used * H * ff * 2 + pairs * (ff * 2 + H * 4), "flops": 2.0 * pairs * H * ff},
+                "router": {"bytes": (E + ident) * H * 4 + Tn * H * 2 + pairs * H * 4 + Tn * H * 4, "flops": 2.0 * Tn * H * (E + ident)},
+                "activation": {"bytes": pairs * 3 * ff * 2, "flops": 0},
+                "norm": {"bytes": Tn * H * (2 + 2 + 4 + 4 + 2), "flops": 0, "per_launch": True},
+                "rotary+write": {"bytes": Tn * (down_cols + qr + row) * 2, "flops": 0, "per_launch": True},
+                "head": {"bytes": V * H * 2 + B * (H * 2 + V * 4), "flops": 2.0 * B * H * V},
+                "embed": {"bytes": Tn * H * (2 + 4), "flops": 0},
+            }
+
+        block = {"sizes": z, "models": {}}
+        for name, raw in (("pivinex", raw_p), ("qwen2", raw_q)):
+            cfg = config_from_dict(raw)
+            biggest = 64
+            eng = Engine(config=cfg, seed=0, dtype="bfloat16", device="cuda:0", page_size=PAGE_SIZE,
+                         max_cache_tokens=biggest * (ctx_len + 256) + 4 * T, max_num_seqs=biggest + 1, max_num_batched_tokens=T,
+                         prefill_chunk=T, max_model_len=ctx_len + 256)
+            st, cache = eng.stepper, eng.cache
+
+            def ev():
+                return torch.cuda.Event(enable_timing=True)
+
+            def prompt(rid, n=T):
+                cache.begin(rid)
+                return st.step([StepEntry(rid, rng.integers(0, V, n).tolist(), [n - 1])])
+
+            for i in range(2):
+                prompt(("warm", i))
+                cache.end(("warm", i))
+            times = []
+            for i in range(reps):
+                a, b = ev(), ev()
+                a.record()
+                prompt(("pf", i))
+                b.record()
+                torch.cuda.synchronize()
+                times.append(a.elapsed_time(b))
+                cache.end(("pf", i))
+            res = {"prefill_ms": round(sorted(times)[len(times) // 2], 3)}
+            res["prefill_tok_s"] = round(T / res["prefill_ms"] * 1e3, 1)
+            with st.kernel_timing() as timer:
+                prompt("timed")
+            cache.end("timed")
+            work = work_pivinex(T, 1, 0) if name == "pivinex" else class_work(raw_q, L, T, 1, 0, 1)
+            res["prefill_kernels"] = kernel_table(timer.totals(), work, res["prefill_ms"] * 1e3, peaks)
+            for i in range(biggest):
+                prompt(("d", i), ctx_len)
+            for B in (8, 64):
+                reqs = [("d", i) for i in range(B)]
+                step = lambda: st.step([StepEntry(r, [int(rng.integers(0, V))], [0]) for r in reqs])
+                for _ in range(max(4, args.warmup)):
+                    step()
+                torch.cuda.synchronize()
+                n = min(args.steps, 32)
+                a, b = ev(), ev()
+                a.record()
+                for _ in range(n):
+                    step()
+                b.record()
+                torch.cuda.synchronize()
+                ms = a.elapsed_time(b) / n
+                res[f"decode_b{B}_ms"] = round(ms, 4)
+                res[f"decode_b{B}_tok_s"] = round(B / ms * 1e3, 1)
+                with st.kernel_timing() as timer:
+                    step()
+                work = work_pivinex(B, B, ctx_len + 40) if name == "pivinex" else class_work(raw_q, L, B, B, ctx_len + 40, B)
+                res[f"decode_b{B}_kernels"] = kernel_table(timer.totals(), work, ms * 1e3, peaks)
+            block["models"][name] = res
+            del eng, st, cache
+            torch.cuda.empty_cache()
+        out["sizes"][tag] = block
+    return out
+
+
 def run_sweep(args) -> dict:
     """Decode throughput over a grid of batch sizes and context lengths and prefill throughput over
     several portion lengths on the 7B shape, each with its fraction of the roofline (device-timed,
@@ -772,10 +900,10 @@ def main() -> int:
                     help="leave out the points at longer contexts and at the 14B and 32B shapes")
     ap.add_argument("--no-per-kernel", action="store_true",
                     help="leave out the `kernels` block (device time, bytes or flops and fraction of the peak per kernel class)")
-    ap.add_argument("--workload", choices=["serve14b", "mixed32b", "sweep", "modovik"], default=None,
+    ap.add_argument("--workload", choices=["serve14b", "mixed32b", "sweep", "modovik", "pivinex"], default=None,
                     help="run one of the two other baseline workloads, a sweep over batch sizes, context lengths and "
-                         "portion lengths on the 7B shape, or the Modovik design beside the Qwen2.5 decoder at equal "
-                         "layer sizes, instead (prints its own JSON line)")
+                         "portion lengths on the 7B shape, or the Modovik or the Pivinex design beside the Qwen2.5 decoder at "
+                         "equal layer sizes, instead (prints its own JSON line)")
     ap.add_argument("--cache-fraction", type=float, default=1.0,
                     help="serve14b: cache capacity as a fraction of what all requests need at once (< 1 forces preemption)")
     args = ap.parse_args()
@@ -783,7 +911,8 @@ def main() -> int:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported, run with --gpus 1")
         return 2
     if args.workload:
-        result = run_sweep(args) if args.workload == "sweep" else run_modovik(args) if args.workload == "modovik" else run_workload(args)
+        result = run_sweep(args) if args.workload == "sweep" else run_modovik(args) if args.workload == "modovik" else \
+            run_pivinex(args) if args.workload == "pivinex" else run_workload(args)
         result["env"] = environment()
         print(json.dumps(result))
         return 0

@@ -272,12 +272,23 @@ __global__ void route_kernel(const T* h, const float* w, const float* correction
     const T* hr = h + (size_t)t * H;
     float* z = z_smem;
     float* choice = z_smem + n_out;
+    // a lane's terms are those of columns lane, lane + 32, ... whichever way they are fetched: one order of sums
+    const bool vec = H % 128 == 0 && (((uintptr_t)hr | (uintptr_t)w) & 15) == 0;
     for (int e = warp; e < n_out; e += warps) {
         const float* wr = w + (size_t)e * H;
-        float acc = 0.f;
-        for (int i = lane; i < H; i += 32) acc = fmaf(to_f32<T>(hr[i]), wr[i], acc);
-        acc = warp_sum(acc);
-        if (lane == 0) z[e] = acc;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        if (vec) {
+            for (int i = lane * 4; i < H; i += 128) {
+                const Vec<T, 4> hv = load_vec<T, 4>(hr + i);
+                const Vec<float, 4> wv = load_vec<float, 4>(wr + i);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) acc[k] = fmaf(to_f32<T>(hv.v[k]), wv.v[k], acc[k]);
+            }
+        } else {
+            for (int i = lane; i < H; i += 32) acc[0] = fmaf(to_f32<T>(hr[i]), wr[i], acc[0]);
+        }
+        const float sum = warp_sum((acc[0] + acc[1]) + (acc[2] + acc[3]));
+        if (lane == 0) z[e] = sum;
     }
     __syncthreads();
     if (warp == 0) {
@@ -327,7 +338,7 @@ PYRE_API int pyre_route(const void* h, const float* w, const float* correction, 
     if (H <= 0 || n_out <= 0 || top <= 0 || top > n_out) return PYRE_ERR_BAD_ARG;
     const size_t smem = (size_t)2 * n_out * sizeof(float);
     if (smem > 48 * 1024) return PYRE_ERR_UNSUPPORTED;
-    const int threads = 256;
+    const int threads = n_tokens >= 512 ? 256 : 1024;      // few tokens: more warps per token's outputs
     if (dtype == PYRE_BF16)
         pyre_launch(route_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), smem, stream, (const __nv_bfloat16*)h, w, correction,
                     idx_out, weight_out, H, n_out, top, scale);

@@ -281,8 +281,8 @@ PYRE_API int pyre_latent_attention_exact(const void* qa, const void* cache, void
 // of the tile's window travel through shared memory in tiles of 32 rows (cp.async, two buffers); a cached row is
 // the key (all `kd` entries, S = Q K^T) and, by its first `rank` entries, the value (O += P V, the B operand
 // fetched with ldmatrix.trans from the same tile).  Softmax online in fp32; P enters the second product as bf16.
-// A CTA holds the output columns [128 z, 128 z + 128) of its rows (blockIdx.z); latents wider than 128 recompute S
-// per 128 columns.  With `n_splits` > 1 the key tiles of a row tile are shared among that many CTAs, which leave
+// A warp holds 128 output columns of its 16 rows; a latent wider than that takes more warps per row group (up to
+// four: 16 warps per CTA), which share the key tiles in shared memory and each recompute S.  With `n_splits` > 1 the key tiles of a row tile are shared among that many CTAs, which leave
 // unnormalised partial outputs with their maxima and sums in scratch memory for the combining kernel.
 //   qa [T, nh, row] absorbed queries (zeros beyond kd); cache [page][page_size][row]; out [T, nh, rank]
 //   row % 16 == 0 (the padding of queries and cache rows is zero, so it adds nothing to a score)
@@ -309,7 +309,7 @@ __device__ __forceinline__ uint32_t lm_pack(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-__global__ void __launch_bounds__(128) latent_attention_mma_kernel(
+__global__ void __launch_bounds__(512) latent_attention_mma_kernel(
     const __nv_bfloat16* qa, const __nv_bfloat16* cache, __nv_bfloat16* out, float* part_o, float* part_ml,
     const int* block_table, int bt_stride, const int* cu_seqlens, const int* positions, int n_seqs, int nh, int hg, int rank,
     int row, int page_size, int window, float scale_log2, int n_splits, int max_len, long long n_pages, int* err_flag) {
@@ -342,8 +342,10 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
     if (seq < 0) return;
     const int tok0 = item[1], ntok = item[2];
     const int h0 = blockIdx.y * hg, nhere = min(hg, nh - h0);
-    const int split = blockIdx.z % n_splits, chunk = blockIdx.z / n_splits;
-    const int c0 = chunk * LM_DV;                                // first output column of this CTA
+    const int lane = threadIdx.x & 31, warp_all = threadIdx.x >> 5;
+    const int warp = warp_all & 3, chunk = warp_all >> 2;        // the warp's 16 rows; its 128 output columns
+    const int split = blockIdx.z;
+    const int c0 = chunk * LM_DV;                                // first output column of this warp
     const int p_first = positions[tok0];
     const int k_hi = p_first + ntok - 1;
     const int k_lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
@@ -352,7 +354,6 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
     const int per = (tiles_total + n_splits - 1) / n_splits;
     const int tile_lo = split * per, tile_hi = min(tiles_total, tile_lo + per);
     const int* table = block_table + (size_t)seq * bt_stride;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int vecs = row / 8;                                    // 16-byte pieces of a row
 
     // the queries of the tile's rows
@@ -399,6 +400,7 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[i][e] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    const bool warp_live = warp * 16 < ntok * hg;                // rows beyond the tile's tokens: nothing to compute
     const int nt_live = min(LM_DV, ((rank - c0 + 7) / 8) * 8) / 8;      // 8-column tiles of the output that exist here
 
     if (tile_lo < tile_hi) load_keys(0, tile_lo);
@@ -412,11 +414,16 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
         }
         __syncthreads();
         const __nv_bfloat16* kt = k_s + (size_t)buf * LM_KT * ld;
+        if (!warp_live) {
+            __syncthreads();
+            continue;
+        }
         float s[LM_KT / 8][4];
 #pragma unroll
         for (int i = 0; i < LM_KT / 8; ++i)
 #pragma unroll
             for (int e = 0; e < 4; ++e) s[i][e] = 0.f;
+#pragma unroll 2
         for (int kk = 0; kk < row; kk += 16) {
             uint32_t a[4], b[LM_KT / 16][4];
             lm_ldmatrix_x4(a, q_s + (warp * 16 + (lane & 15)) * ld + kk + (lane >> 4) * 8);
@@ -562,8 +569,9 @@ PYRE_API int pyre_latent_attention_mma(const void* qa, const void* cache, void* 
         attr_set[dev] = true;
     }
     const int chunks = ceil_div(rank, LM_DV);
+    if (chunks > 4) return PYRE_ERR_UNSUPPORTED;
     const float scale_log2 = scale * 1.4426950408889634f;
-    pyre_launch(latent_attention_mma_kernel, dim3(n_tiles, ceil_div(nh, hg), chunks * n_splits), dim3(128), smem, stream,
+    pyre_launch(latent_attention_mma_kernel, dim3(n_tiles, ceil_div(nh, hg), n_splits), dim3(128 * chunks), smem, stream,
                 (const __nv_bfloat16*)qa, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, part_o, part_ml, block_table, bt_stride,
                 cu_seqlens, positions, n_seqs, nh, hg, rank, row, page_size, window, scale_log2, n_splits, max_len, n_pages,
                 err_flag);

@@ -1597,7 +1597,7 @@ def combine_pairs(y: torch.Tensor, h: torch.Tensor, place_of: torch.Tensor, weig
 
 LATENT_MMA_ROWS = 64          # (token, head) rows of a CTA of the tensor-core kernel
 LATENT_MMA_KEYS = 32          # cached rows per key tile
-LATENT_MMA_COLS = 128         # output columns per CTA
+LATENT_MMA_COLS = 128         # output columns per warp; up to four such groups of warps per CTA
 USE_LATENT_MMA = True
 
 
@@ -1609,7 +1609,7 @@ def latent_mma_ok(dtype: torch.dtype, row: int) -> bool:
 def latent_attention_splits(n_tiles: int, n_heads: int, rank: int, span: int) -> int:
     """Into how many shares the tensor-core latent attention cuts the keys of every row tile: enough CTAs for about
     one and a half per SM, at least four key tiles per share, at most 16.  ``span``: the most keys a tile walks."""
-    ctas = max(1, n_tiles * -(-n_heads // LATENT_MMA_ROWS) * -(-rank // LATENT_MMA_COLS))
+    ctas = max(1, n_tiles * -(-n_heads // LATENT_MMA_ROWS))      # the column groups of a wide latent are warps of one CTA
     tiles = -(-span // LATENT_MMA_KEYS) + 1
     return int(max(1, min(int(1.5 * sm_count() / ctas), tiles // 4, 16)))
 
