@@ -8,7 +8,7 @@
 //   * the rows are sorted by group, group g owning the sorted places offsets[g] .. offsets[g + 1] (a product per
 //     EXPERT of a routed feed-forward: `src` gathers a place's input row, `dst` says where its result goes).
 //
-// One CTA computes a 64 x 64 tile of a group's result.  float32: FFMA, one chain per output element over k in
+// One CTA computes a 64 x 64 tile of a group's result (128 x 128 for bfloat16 groups of many rows).  float32: FFMA, one chain per output element over k in
 // ascending order, so a row's result does not depend on which other rows share its tile or its launch.
 // bfloat16 operands: the same tiles on the tensor cores (mma.sync m16n8k16, fp32 accumulators).
 // `dtype`: type of x and w (0 = float32, 1 = bfloat16); `out_f32`: the result stays fp32, else it is rounded to dtype.
@@ -31,7 +31,9 @@ struct GroupedArgs {
 constexpr int GB_M = 64, GB_N = 64, GB_K = 16;
 
 // Which (group, first place, places) a CTA works on; false: nothing to do.
+template <int TILE_M = 64>
 __device__ __forceinline__ bool grouped_tile(const GroupedArgs& a, int& g, int& first, int& count) {
+    constexpr int GB_M = TILE_M;
     if (!a.offsets) {
         g = blockIdx.z;
         first = blockIdx.x * GB_M;
@@ -227,6 +229,113 @@ __global__ void __launch_bounds__(128) grouped_linear_mma_kernel(GroupedArgs a) 
         }
 }
 
+// ---------------------------------------------------------------------------
+// The same product for groups of many rows: 128 x 128 tiles, eight warps of 64 x 32 each (16 MMAs per four A and two B
+// fragment loads), K in steps of 32 through two buffers filled by cp.async while the other is multiplied.
+// ---------------------------------------------------------------------------
+constexpr int GL_M = 128, GL_N = 128;
+
+__global__ void __launch_bounds__(256) grouped_linear_mma_large_kernel(GroupedArgs a) {
+    __shared__ __align__(16) __nv_bfloat16 xs[2][GL_M][GT_LD];
+    __shared__ __align__(16) __nv_bfloat16 ws[2][GL_N][GT_LD];
+    __shared__ int src_row[GL_M], dst_row[GL_M];
+    pdl_trigger();
+    pdl_wait();
+    int g, first, count;
+    if (!grouped_tile<GL_M>(a, g, first, count)) return;
+    const int n0 = blockIdx.y * GL_N;
+    if (threadIdx.x < GL_M) {
+        const int p = first + threadIdx.x;
+        const bool live = (int)threadIdx.x < count;
+        src_row[threadIdx.x] = live ? (a.src ? a.src[p] : p) : -1;
+        dst_row[threadIdx.x] = live ? (a.dst ? a.dst[p] : p) : -1;
+    }
+    __syncthreads();
+    const __nv_bfloat16* x = (const __nv_bfloat16*)a.x + (size_t)g * a.x_group_stride;
+    const __nv_bfloat16* w = (const __nv_bfloat16*)a.w + (size_t)g * a.w_group_stride;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int wm = (warp >> 2) * 64, wn = (warp & 3) * 32;
+    float acc[4][4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.f;
+
+    // a stage: 128 rows x 32 k of each operand = 512 pieces of 16 bytes per operand, two per thread and operand
+    auto load_stage = [&](int st, int k0) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int idx = threadIdx.x + u * 256;
+            const int r = idx >> 2, k = (idx & 3) * 8;
+            const int sr = src_row[r];
+            __nv_bfloat16* xd = &xs[st][r][k];
+            __nv_bfloat16* wd = &ws[st][r][k];
+            if (sr >= 0 && k0 + k < a.K) {
+                const uint32_t d = (uint32_t)__cvta_generic_to_shared(xd);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(x + (size_t)sr * a.x_row_stride + k0 + k));
+            } else {
+                *reinterpret_cast<uint4*>(xd) = make_uint4(0, 0, 0, 0);
+            }
+            if (n0 + r < a.N && k0 + k < a.K) {
+                const uint32_t d = (uint32_t)__cvta_generic_to_shared(wd);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(w + (size_t)(n0 + r) * a.K + k0 + k));
+            } else {
+                *reinterpret_cast<uint4*>(wd) = make_uint4(0, 0, 0, 0);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::);
+    };
+    const int n_steps = (a.K + GT_K - 1) / GT_K;
+    load_stage(0, 0);
+    for (int s = 0; s < n_steps; ++s) {
+        const int st = s & 1;
+        if (s + 1 < n_steps) {
+            load_stage(st ^ 1, (s + 1) * GT_K);
+            asm volatile("cp.async.wait_group 1;" ::);
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < GT_K; kk += 16) {
+            uint32_t af[4][4], bf[2][4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                ldmatrix_x4(af[i], &xs[st][wm + i * 16 + (lane & 15)][kk + (lane >> 4) * 8]);
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+                ldmatrix_x4(bf[j], &ws[st][wn + j * 16 + (lane & 7) + ((lane >> 4) << 3)][kk + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) mma_bf16(acc[i][j], af[i], bf[j >> 1][(j & 1) * 2], bf[j >> 1][(j & 1) * 2 + 1]);
+        }
+        __syncthreads();      // the buffer is filled again two steps on
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int dr = dst_row[wm + i * 16 + (lane >> 2) + half * 8];
+            if (dr < 0) continue;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int n = n0 + wn + j * 8 + (lane & 3) * 2;
+                const size_t at = (size_t)dr * a.out_row_stride + (size_t)g * a.out_group_stride + n;
+                const float v0 = acc[i][j][half * 2], v1 = acc[i][j][half * 2 + 1];
+                if (a.out_f32) {
+                    if (n < a.N) ((float*)a.out)[at] = v0;
+                    if (n + 1 < a.N) ((float*)a.out)[at + 1] = v1;
+                } else {
+                    if (n < a.N) ((__nv_bfloat16*)a.out)[at] = __float2bfloat16_rn(v0);
+                    if (n + 1 < a.N) ((__nv_bfloat16*)a.out)[at + 1] = __float2bfloat16_rn(v1);
+                }
+            }
+        }
+}
+
 // places: an upper bound of the sorted places (the host does not know the groups' sizes); with offsets == null it is unused
 PYRE_API int pyre_grouped_linear(const void* x, long long x_row_stride, long long x_group_stride, const void* w,
                                  long long w_group_stride, void* out, long long out_row_stride, long long out_group_stride,
@@ -246,7 +355,14 @@ PYRE_API int pyre_grouped_linear(const void* x, long long x_row_stride, long lon
     if (dtype == PYRE_BF16 && use_mma) {
         if (K % 8 || x_row_stride % 8 || x_group_stride % 8 || w_group_stride % 8 || (((uintptr_t)x | (uintptr_t)w) & 15))
             return PYRE_ERR_UNSUPPORTED;
-        pyre_launch(grouped_linear_mma_kernel, grid, dim3(128), 0, stream, a);
+        // groups of about a hundred rows or more (a prompt portion's heads or experts): the large tiles
+        const long long rows_per_group = offsets ? (long long)places / G : M;
+        if (rows_per_group >= 96) {
+            const dim3 big = offsets ? dim3(ceil_div(places, GL_M) + G, ceil_div(N, GL_N), 1) : dim3(ceil_div(M, GL_M), ceil_div(N, GL_N), G);
+            pyre_launch(grouped_linear_mma_large_kernel, big, dim3(256), 0, stream, a);
+        } else {
+            pyre_launch(grouped_linear_mma_kernel, grid, dim3(128), 0, stream, a);
+        }
     } else if (dtype == PYRE_BF16) pyre_launch(grouped_linear_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, a);
     else if (dtype == PYRE_F32) pyre_launch(grouped_linear_kernel<float>, grid, dim3(256), 0, stream, a);
     else return PYRE_ERR_BAD_ARG;
@@ -272,7 +388,7 @@ __global__ void route_kernel(const T* h, const float* w, const float* correction
     const T* hr = h + (size_t)t * H;
     float* z = z_smem;
     float* choice = z_smem + n_out;
-    // a lane's terms are those of columns lane, lane + 32, ... whichever way they are fetched: one order of sums
+    // which columns a lane adds depends on H and the pointers' alignment only, never on the batch
     const bool vec = H % 128 == 0 && (((uintptr_t)hr | (uintptr_t)w) & 15) == 0;
     for (int e = warp; e < n_out; e += warps) {
         const float* wr = w + (size_t)e * H;

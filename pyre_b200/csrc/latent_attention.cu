@@ -282,7 +282,9 @@ PYRE_API int pyre_latent_attention_exact(const void* qa, const void* cache, void
 // the key (all `kd` entries, S = Q K^T) and, by its first `rank` entries, the value (O += P V, the B operand
 // fetched with ldmatrix.trans from the same tile).  Softmax online in fp32; P enters the second product as bf16.
 // A warp holds 128 output columns of its 16 rows; a latent wider than that takes more warps per row group (up to
-// four: 16 warps per CTA), which share the key tiles in shared memory and each recompute S.  With `n_splits` > 1 the key tiles of a row tile are shared among that many CTAs, which leave
+// four: 16 warps per CTA), which share the key tiles in shared memory; the warps of a row group then split the
+// inner dimension of S = Q K^T among them and exchange their partial scores through shared memory (added in a
+// fixed order), so S is computed once.  With `n_splits` > 1 the key tiles of a row tile are shared among that many CTAs, which leave
 // unnormalised partial outputs with their maxima and sums in scratch memory for the combining kernel.
 //   qa [T, nh, row] absorbed queries (zeros beyond kd); cache [page][page_size][row]; out [T, nh, rank]
 //   row % 16 == 0 (the padding of queries and cache rows is zero, so it adds nothing to a score)
@@ -320,6 +322,8 @@ __global__ void __launch_bounds__(512) latent_attention_mma_kernel(
     const int ld = row + 8;                                      // padded row of the shared tiles, in elements
     __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(lm_smem);          // [64][ld]
     __nv_bfloat16* k_s = q_s + LM_ROWS * ld;                                  // [2][32][ld]
+    float* sx = reinterpret_cast<float*>(k_s + 2 * LM_KT * ld);               // [4 row groups][column groups][16][32]: partial scores
+    const int n_cg = blockDim.x >> 7;                                         // column groups = warps per row group
     const int tq = LM_ROWS / hg;                                 // tokens of a row tile
     if (threadIdx.x == 0) {
         int tile = blockIdx.x;
@@ -423,8 +427,10 @@ __global__ void __launch_bounds__(512) latent_attention_mma_kernel(
         for (int i = 0; i < LM_KT / 8; ++i)
 #pragma unroll
             for (int e = 0; e < 4; ++e) s[i][e] = 0.f;
+        const int ks_per = (row / 16 + n_cg - 1) / n_cg;         // k-steps of S per warp of a row group
+        const int kk_lo = chunk * ks_per * 16, kk_hi = min(row, kk_lo + ks_per * 16);
 #pragma unroll 2
-        for (int kk = 0; kk < row; kk += 16) {
+        for (int kk = kk_lo; kk < kk_hi; kk += 16) {
             uint32_t a[4], b[LM_KT / 16][4];
             lm_ldmatrix_x4(a, q_s + (warp * 16 + (lane & 15)) * ld + kk + (lane >> 4) * 8);
 #pragma unroll
@@ -432,6 +438,23 @@ __global__ void __launch_bounds__(512) latent_attention_mma_kernel(
                 lm_ldmatrix_x4(b[j], kt + (j * 16 + (lane & 7) + ((lane >> 4) << 3)) * ld + kk + ((lane >> 3) & 1) * 8);
 #pragma unroll
             for (int i = 0; i < LM_KT / 8; ++i) lm_mma(s[i], a, b[i >> 1][(i & 1) * 2], b[i >> 1][(i & 1) * 2 + 1]);
+        }
+        if (n_cg > 1) {
+            // every warp of the row group gets the whole sums: its own part and the others', in the groups' order
+            float* mine = sx + (size_t)((warp * n_cg + chunk) * 16) * 32;
+#pragma unroll
+            for (int i = 0; i < LM_KT / 8; ++i)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) mine[(i * 4 + e) * 32 + lane] = s[i][e];
+            asm volatile("bar.sync %0, %1;" ::"r"(1 + warp), "r"(32 * n_cg) : "memory");
+#pragma unroll
+            for (int i = 0; i < LM_KT / 8; ++i)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float acc = 0.f;
+                    for (int c = 0; c < n_cg; ++c) acc += sx[(size_t)((warp * n_cg + c) * 16 + i * 4 + e) * 32 + lane];
+                    s[i][e] = acc;
+                }
         }
         // mask, and the tile's row maxima
         const int pos0 = k_al + tile * LM_KT;
@@ -559,7 +582,9 @@ PYRE_API int pyre_latent_attention_mma(const void* qa, const void* cache, void* 
     if (rank <= 0 || row < rank || row % 16 || nh <= 0 || page_size <= 0 || n_splits < 1) return PYRE_ERR_BAD_ARG;
     if (n_splits > 1 && (!part_o || !part_ml)) return PYRE_ERR_BAD_ARG;
     const int hg = min(nh, LM_ROWS);
-    const size_t smem = (size_t)(LM_ROWS + 2 * LM_KT) * (row + 8) * sizeof(__nv_bfloat16);
+    const int chunks = ceil_div(rank, LM_DV);
+    if (chunks > 4) return PYRE_ERR_UNSUPPORTED;
+    const size_t smem = (size_t)(LM_ROWS + 2 * LM_KT) * (row + 8) * sizeof(__nv_bfloat16) + (chunks > 1 ? (size_t)4 * chunks * 16 * 32 * sizeof(float) : 0);
     if (smem > 200 * 1024) return PYRE_ERR_UNSUPPORTED;
     static bool attr_set[PYRE_MAX_DEVICES] = {};
     const int dev = pyre_current_device();
@@ -568,8 +593,6 @@ PYRE_API int pyre_latent_attention_mma(const void* qa, const void* cache, void* 
         if (e != cudaSuccess) return (int)e;
         attr_set[dev] = true;
     }
-    const int chunks = ceil_div(rank, LM_DV);
-    if (chunks > 4) return PYRE_ERR_UNSUPPORTED;
     const float scale_log2 = scale * 1.4426950408889634f;
     pyre_launch(latent_attention_mma_kernel, dim3(n_tiles, ceil_div(nh, hg), n_splits), dim3(128 * chunks), smem, stream,
                 (const __nv_bfloat16*)qa, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, part_o, part_ml, block_table, bt_stride,

@@ -1603,7 +1603,7 @@ USE_LATENT_MMA = True
 
 def latent_mma_ok(dtype: torch.dtype, row: int) -> bool:
     """The sizes the tensor-core latent attention takes (as its launcher checks them)."""
-    return USE_LATENT_MMA and dtype == torch.bfloat16 and row % 16 == 0 and (LATENT_MMA_ROWS + 2 * LATENT_MMA_KEYS) * (row + 8) * 2 <= 200 * 1024
+    return USE_LATENT_MMA and dtype == torch.bfloat16 and row % 16 == 0 and (LATENT_MMA_ROWS + 2 * LATENT_MMA_KEYS) * (row + 8) * 2 + 32 * 1024 <= 200 * 1024
 
 
 def latent_attention_splits(n_tiles: int, n_heads: int, rank: int, span: int) -> int:

@@ -111,7 +111,8 @@ def test_latent_norms_rotation_and_paged_write(ops, dtype, q_rank, rank, rope, r
 
 @pytest.mark.parametrize("dtype", BOTH)
 @pytest.mark.parametrize("mma", [False, True])
-@pytest.mark.parametrize("T,Hn,K,N,xs,os_", [(5, 3, 16, 24, 24, 32), (130, 4, 32, 48, 48, 64), (70, 5, 20, 36, 32, 36), (1, 8, 64, 192, 96, 224)])
+@pytest.mark.parametrize("T,Hn,K,N,xs,os_", [(5, 3, 16, 24, 24, 32), (130, 4, 32, 48, 48, 64), (70, 5, 20, 36, 32, 36), (1, 8, 64, 192, 96, 224),
+                                             (300, 3, 72, 200, 80, 208)])
 def test_a_product_per_head(ops, dtype, mma, T, Hn, K, N, xs, os_, monkeypatch):
     monkeypatch.setattr(ops, "USE_GROUPED_MMA", mma)
     x, w = bf16_exact(T, Hn, xs, seed=21), bf16_exact(Hn, N, K, seed=22)
@@ -225,7 +226,7 @@ def test_latent_attention_kernels(ops, kernel, nh, rank, rope, page, window):
 @pytest.mark.parametrize("dtype", BOTH)
 @pytest.mark.parametrize("mma", [False, True])
 @pytest.mark.parametrize("T,Hn,ff,E,ident,top,scale", [(1, 96, 64, 5, 1, 2, 1.0), (77, 92, 24, 3, 2, 3, 0.7), (300, 256, 128, 8, 0, 2, 1.5),
-                                                       (9, 64, 32, 4, 0, 1, 2.5), (40, 128, 16, 1, 3, 2, 1.0)])
+                                                       (9, 64, 32, 4, 0, 1, 2.5), (40, 128, 16, 1, 3, 2, 1.0), (700, 128, 192, 4, 1, 2, 1.0)])
 def test_routed_feed_forward_step_by_step(ops, dtype, mma, T, Hn, ff, E, ident, top, scale, monkeypatch):
     """Router (scores over all outputs, a correction that only the choice sees, weights not renormalised), the sort by
     expert, both products per expert and the weighted sum, outputs without weights included, against the plain
