@@ -368,21 +368,21 @@ __global__ void __launch_bounds__(512) latent_attention_mma_kernel(
         if (tt < ntok && hh < nhere) val = *reinterpret_cast<const uint4*>(qa + ((size_t)(tok0 + tt) * nh + h0 + hh) * row + v * 8);
         *reinterpret_cast<uint4*>(q_s + r * ld + v * 8) = val;
     }
+    // a thread fetches pieces of ONE cached row per tile (blockDim / 32 threads share a row): one look at the block
+    // table per thread and tile
+    const int tpr = blockDim.x / LM_KT, key_j = threadIdx.x / tpr, key_v = threadIdx.x - key_j * tpr;
     auto load_keys = [&](int buf, int tile) {
-        __nv_bfloat16* dst = k_s + (size_t)buf * LM_KT * ld;
-        const int pos0 = k_al + tile * LM_KT;
-        for (int idx = threadIdx.x; idx < LM_KT * vecs; idx += blockDim.x) {
-            const int j = idx / vecs, v = idx - j * vecs;
-            const int pos = pos0 + j;
-            __nv_bfloat16* d = dst + j * ld + v * 8;
-            if (pos >= k_lo && pos <= k_hi) {
-                const int page = pyre_checked_page(table[pos / page_size], n_pages, err_flag);
-                const __nv_bfloat16* src = cache + ((size_t)page * page_size + pos % page_size) * row + v * 8;
-                const uint32_t daddr = (uint32_t)__cvta_generic_to_shared(d);
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(daddr), "l"(src));
-            } else {
-                *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+        __nv_bfloat16* d = k_s + (size_t)buf * LM_KT * ld + key_j * ld;
+        const int pos = k_al + tile * LM_KT + key_j;
+        if (pos >= k_lo && pos <= k_hi) {
+            const int page = pyre_checked_page(table[pos / page_size], n_pages, err_flag);
+            const __nv_bfloat16* src = cache + ((size_t)page * page_size + pos % page_size) * row;
+            for (int v = key_v; v < vecs; v += tpr) {
+                const uint32_t daddr = (uint32_t)__cvta_generic_to_shared(d + v * 8);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(daddr), "l"(src + v * 8));
             }
+        } else {
+            for (int v = key_v; v < vecs; v += tpr) *reinterpret_cast<uint4*>(d + v * 8) = make_uint4(0, 0, 0, 0);
         }
         asm volatile("cp.async.commit_group;" ::);
     };
@@ -450,22 +450,31 @@ __global__ void __launch_bounds__(512) latent_attention_mma_kernel(
 #pragma unroll
             for (int i = 0; i < LM_KT / 8; ++i)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    float acc = 0.f;
-                    for (int c = 0; c < n_cg; ++c) acc += sx[(size_t)((warp * n_cg + c) * 16 + i * 4 + e) * 32 + lane];
-                    s[i][e] = acc;
-                }
+                for (int e = 0; e < 4; ++e) s[i][e] = 0.f;
+            for (int c = 0; c < n_cg; ++c) {
+                const float* part = sx + (size_t)((warp * n_cg + c) * 16) * 32 + lane;
+#pragma unroll
+                for (int i = 0; i < LM_KT / 8; ++i)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) s[i][e] += part[(i * 4 + e) * 32];
+            }
         }
         // mask, and the tile's row maxima
         const int pos0 = k_al + tile * LM_KT;
         float mx[2] = {-INFINITY, -INFINITY};
+        // a tile that every token of the CTA sees whole (after the last token's window starts, before the first token's
+        // own position ends) needs no mask
+        const bool whole = pos0 + LM_KT - 1 <= p_first && (window <= 0 || pos0 >= k_hi - window + 1);
 #pragma unroll
         for (int i = 0; i < LM_KT / 8; ++i)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int u = e >> 1;
-                const int pos = pos0 + i * 8 + (lane & 3) * 2 + (e & 1);
-                const bool ok = live[u] && pos >= lo_row[u] && pos <= p_row[u];
+                bool ok = live[u];
+                if (!whole) {
+                    const int pos = pos0 + i * 8 + (lane & 3) * 2 + (e & 1);
+                    ok = ok && pos >= lo_row[u] && pos <= p_row[u];
+                }
                 s[i][e] = ok ? s[i][e] * scale_log2 : -INFINITY;
                 mx[u] = fmaxf(mx[u], s[i][e]);
             }
@@ -494,10 +503,13 @@ __global__ void __launch_bounds__(512) latent_attention_mma_kernel(
             sum[u] += __shfl_xor_sync(0xffffffffu, sum[u], 2);
             l[u] = l[u] * alpha[u] + sum[u];
         }
+        // the maxima seldom move after the first tiles: rescale only when a row of the warp needs it
+        if (__any_sync(0xffffffffu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {
 #pragma unroll
-        for (int i = 0; i < LM_DV / 8; ++i) {
-            o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
-            o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+            for (int i = 0; i < LM_DV / 8; ++i) {
+                o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+                o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+            }
         }
         // O += P V: the tile's rows again, their entries c0 .. as values
 #pragma unroll

@@ -255,7 +255,8 @@ def collect_tensors(part: Part, prefix: str = "") -> dict[str, TensorSpec]:
 
 
 def load_part(part: Part, tensors: Mapping[str, torch.Tensor], prefix: str = "") -> None:
-    part.load({name: tensors[prefix + name] for name in part.tensors()})
+    part.load({name: tensors[prefix + name] for name, spec in part.tensors().items()
+               if prefix + name in tensors or not getattr(spec, "optional", False)})
     for sub_prefix, child in part.children().items():
         load_part(child, tensors, prefix + sub_prefix)
 

@@ -142,8 +142,8 @@ class ParallelBlock(Part):
         if not self.layer_scale:
             return {}
         t = {self.names["ls1"]: TensorSpec((self.width,), role="vector", init=("normal", 1.0, 0.1))}
-        if self.ffn is not None:
-            t[self.names["ls2"]] = TensorSpec((self.width,), role="vector", init=("normal", 1.0, 0.1))
+        # a layer without a feed-forward has no use for the second gain; a checkpoint may hold it all the same
+        t[self.names["ls2"]] = TensorSpec((self.width,), role="vector", init=("normal", 1.0, 0.1), optional=self.ffn is None)
         return t
 
     def load(self, tensors):

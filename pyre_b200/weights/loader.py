@@ -64,6 +64,8 @@ def check_names_and_shapes(expected: Mapping[str, TensorSpec], found: Mapping[st
         if name not in found:
             if spec.optional_alias is not None and spec.optional_alias in found:
                 continue
+            if spec.optional:
+                continue
             missing.append(name)
             continue
         shape = tuple(found[name][0])
@@ -125,6 +127,6 @@ def load_tensors(model_dir: str | Path, expected: Mapping[str, TensorSpec], comp
                 if sink is not None:
                     sink(name, t)
     for name, spec in expected.items():
-        if name not in out:
+        if name not in out and not (spec.optional and spec.optional_alias is None):
             out[name] = out[spec.optional_alias]
     return out

@@ -54,8 +54,8 @@ def random_state(config: ModelConfig, seed: int, store_dtype: torch.dtype = torc
     gen.manual_seed(int(seed))
     state = {}
     for name, spec in expected_tensors(config).items():
-        if spec.optional_alias is not None:
-            continue  # tied: the alias stands in, nothing is stored
+        if spec.optional_alias is not None or spec.optional:
+            continue  # tied: the alias stands in, nothing is stored; optional: a checkpoint need not hold it
         dtype = torch.int32 if spec.role == "int" else store_dtype
         state[name] = _draw(spec, gen, "cpu", dtype)
     return state
@@ -75,7 +75,7 @@ def random_tensors_on_device(expected: Mapping[str, TensorSpec], seed: int, comp
                              device, sink=None) -> dict[str, torch.Tensor]:
     out: dict[str, torch.Tensor] = {}
     for name, spec in expected.items():
-        if spec.optional_alias is not None:
+        if spec.optional_alias is not None or spec.optional:
             continue
         gen = torch.Generator(device=device)
         gen.manual_seed((int(seed) << 32) ^ zlib.crc32(name.encode()))
@@ -86,6 +86,6 @@ def random_tensors_on_device(expected: Mapping[str, TensorSpec], seed: int, comp
         if sink is not None:
             sink(name, t)
     for name, spec in expected.items():
-        if name not in out:
+        if name not in out and not spec.optional:
             out[name] = out[spec.optional_alias]
     return out

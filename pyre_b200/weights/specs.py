@@ -21,9 +21,12 @@ class TensorSpec:
     ``init``: ``("normal", mean, std)`` for the random-weights mode.
     ``optional_alias``: name of another tensor that stands in when this one is absent
     (a tied output head reads the embedding table).
+    ``optional``: the checkpoint may or may not hold the tensor (a gain for a branch that the layer does not have);
+    when it is absent the part's ``load`` simply does not get it, and the random-weights mode does not write it.
     """
 
     shape: tuple[int, ...]
     role: str = "matrix"
     init: tuple = ("normal", 0.0, 0.02)
     optional_alias: str | None = None
+    optional: bool = False

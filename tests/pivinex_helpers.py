@@ -44,7 +44,7 @@ PIV_A = {"architecture": "Pivinex", "vocab": 300, "width": 96, "norm": {"eps": 1
 #    product for odd K, the scalar paths, the exact attention kernel in both dtypes), only part of the rotated part
 #    rotated, a window of 7 on pages of 8, no repeated span, as many chosen as there are experts with weights.
 PIV_B = {"architecture": "Pivinex", "vocab": 333, "width": 92, "norm": {"eps": 3e-6}, "residual_mult": 1.0, "layers": [
-    _layer(_mixer(5, 20, 12, 12, 20, 36, 0.18, 7, base=500.0, rot_dims=8), _moe(24, 3, 2, 3, 0.7)),
+    _layer(_mixer(5, 20, 12, 12, 20, 36, 0.18, 7, base=500.0, rot_dims=8), _moe(20, 3, 2, 3, 0.7)),
     _layer(_mixer(5, 20, 12, 12, 20, 36, 0.18, 7, base=500.0, rot_dims=8), _dense(66)),
     _layer(_mixer(2, 28, 4, 40, 12, 52, 0.3, 1000)),
 ]}
@@ -55,10 +55,11 @@ PIV_C = {"architecture": "Pivinex", "vocab": 640, "width": 256, "norm": {"eps": 
     _layer(_mixer(8, 64, 32, 64, 96, 192, 0.09, 64, base=1000000.0), _dense(512)),
     _layer(_mixer(8, 64, 32, 64, 96, 192, 0.09, 64, base=1000000.0), _moe(128, 8, 0, 2, 1.0)),
 ]}
-# D: more heads than a row tile of the attention kernel takes (72 > 64), a latent of 64 with a key part of 16,
-#    a window far wider than any request (all keys), one layer.
+# D: more heads than a row tile of the attention kernel takes (72 > 64), a latent of 64 with a key part of 16, a query
+#    latent of 36 (a stacked down-projection of 116 rows, no multiple of 8, on the tensor-core product; the queries'
+#    up-projection with an inner size of 36 on the library product), a window far wider than any request, one layer.
 PIV_D = {"architecture": "Pivinex", "vocab": 256, "width": 128, "norm": {"eps": 1e-5}, "residual_mult": 0.8, "layers": [
-    _layer(_mixer(72, 16, 16, 8, 32, 64, 0.2, 100000), _dense(128)),
+    _layer(_mixer(72, 16, 16, 8, 36, 64, 0.2, 100000), _dense(128)),
 ]}
 PIV = {"A": PIV_A, "B": PIV_B, "C": PIV_C, "D": PIV_D}
 PIV_PAGE_SIZE = {"A": 16, "B": 8, "C": 32, "D": 16}

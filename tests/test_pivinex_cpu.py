@@ -53,7 +53,7 @@ def test_tensor_names_and_cache_groups():
     table = tensor_table(spec)
     assert {"embed", "embed.norm", "head", "final.norm", "l0.norm1", "l0.ls1", "l0.ls2", "l0.mix.dq", "l0.mix.dq.norm",
             "l0.mix.dkv.norm", "l0.mlp.gate", "l1.mlp.e4.down", "l1.mlp.router", "l1.mlp.correction", "l2.ls1", "l3.mlp.e3.up"} <= set(table)
-    assert "l2.ls2" not in table and "l2.mlp.gate" not in table and "l1.mlp.e5.gate" not in table and "l0.norm2" not in table
+    assert table["l2.ls2"].optional and not table["l1.ls2"].optional and "l2.mlp.gate" not in table and "l1.mlp.e5.gate" not in table and "l0.norm2" not in table
     assert table["l1.mlp.router"].shape == (6, 96) and table["l3.mlp.correction"].shape == (4,)
     assert table["l0.mix.dkv"].shape == (24 + 8, 96) and table["l0.mix.uq"].shape == (3 * (16 + 8), 40)
     assert table["l1.mix.uk"].shape == (4 * 32, 48) and table["l1.mix.uv"].shape == (4 * 16, 48)
@@ -125,6 +125,21 @@ def test_a_window_gives_its_pages_back(monkeypatch, folders):
     assert held == {11: 1, 23: 2}, held        # positions 79..89 and 67..89 on pages of 16
     cache.end("w")
     cache.check()
+
+
+def test_a_layer_without_a_feed_forward_may_hold_its_second_gain(tmp_path, monkeypatch, folders):
+    """The random mode leaves the unused gain out; a checkpoint that holds it loads as well and computes the same."""
+    from safetensors.torch import load_file, save_file
+    from pyre_b200.models.model import load_model
+    standins.install(monkeypatch)
+    d, _reqs, _plain = folders["A"]
+    state = load_file(str(d / "model.safetensors"))
+    assert "l2.ls2" not in state
+    state["l2.ls2"] = torch.full((96,), 3.0)
+    (tmp_path / "config.json").write_text((d / "config.json").read_text())
+    save_file(state, str(tmp_path / "model.safetensors"))
+    model, _ = load_model(tmp_path, "cpu", "float32")
+    assert model.loaded and model.blocks[2].gain2 is None
 
 
 def test_random_model_folder_loads(tmp_path, monkeypatch):
