@@ -158,8 +158,8 @@ def paged(rows_of, page, row, dtype, first_live=None, seed=0):
 
 
 @pytest.mark.parametrize("kernel", ["exact32", "exact16", "mma"])
-@pytest.mark.parametrize("nh,rank,rope,page,window", [(3, 24, 8, 16, 11), (6, 128, 32, 16, 40), (8, 192, 32, 32, 64), (72, 64, 16, 8, 0),
-                                                      (5, 36, 12, 8, 7), (2, 272, 16, 16, 300)])
+@pytest.mark.parametrize("nh,rank,rope,page,window", [(3, 24, 8, 16, 11), (7, 112, 16, 16, 33), (8, 192, 32, 32, 64), (72, 64, 16, 8, 0),
+                                                      (5, 36, 12, 8, 7), (2, 272, 16, 16, 300), (4, 38, 12, 16, 9)])
 def test_latent_attention_kernels(ops, kernel, nh, rank, rope, page, window):
     """Entries of many lengths in one launch (single tokens, portions that start in the middle of a page and of a
     window, one from position 0), each token against the plain softmax over exactly its window.  In every sequence
