@@ -1606,12 +1606,18 @@ def latent_mma_ok(dtype: torch.dtype, row: int) -> bool:
     return USE_LATENT_MMA and dtype == torch.bfloat16 and row % 16 == 0 and (LATENT_MMA_ROWS + 2 * LATENT_MMA_KEYS) * (row + 8) * 2 + 32 * 1024 <= 200 * 1024
 
 
-def latent_attention_splits(n_tiles: int, n_heads: int, rank: int, span: int) -> int:
-    """Into how many shares the tensor-core latent attention cuts the keys of every row tile: enough CTAs for about
-    one and a half per SM, at least four key tiles per share, at most 16.  ``span``: the most keys a tile walks."""
+def latent_attention_splits(n_tiles: int, n_heads: int, rank: int, span: int, row: "int | None" = None) -> int:
+    """Into how many shares the tensor-core latent attention cuts the keys of every row tile: as many as fill the CTAs
+    that are resident at once (its shared memory and threads allow one to a few per SM: whole rounds, since a second
+    round of CTAs costs as much as the first), at least four key tiles per share, at most 16.  ``span``: the most keys
+    a tile walks; ``row``: entries of a cached row (default: the latent and a rotated part of a quarter of it)."""
     ctas = max(1, n_tiles * -(-n_heads // LATENT_MMA_ROWS))      # the column groups of a wide latent are warps of one CTA
+    groups = -(-rank // LATENT_MMA_COLS)
+    row = row if row is not None else -(-(rank + rank // 4) // 16) * 16
+    smem = (LATENT_MMA_ROWS + 2 * LATENT_MMA_KEYS) * (row + 8) * 2 + (4 * groups * 16 * 32 * 4 if groups > 1 else 0)
+    resident = sm_count() * max(1, min(227 * 1024 // smem, 2048 // (128 * groups), 4))
     tiles = -(-span // LATENT_MMA_KEYS) + 1
-    return int(max(1, min(int(1.5 * sm_count() / ctas), tiles // 4, 16)))
+    return int(max(1, min(resident // ctas, tiles // 4, 16)))
 
 
 def latent_attention_mma(qa: torch.Tensor, cache_layer: torch.Tensor, block_table: torch.Tensor, cu_seqlens: torch.Tensor,
@@ -1658,4 +1664,4 @@ def latent_attention(ctx, qa: torch.Tensor, cache_layer: torch.Tensor, block_tab
     n_tiles = int((-(-lens // tq)).sum())
     span = ctx.max_context if not window else min(ctx.max_context, window + tq)
     return latent_attention_mma(qa, cache_layer, block_table, ctx.cu_seqlens, ctx.positions, n_tiles, rank, scale, window,
-                                latent_attention_splits(n_tiles, nh, rank, span))
+                                latent_attention_splits(n_tiles, nh, rank, span, row))

@@ -97,7 +97,7 @@ class LatentAttention(Part):
             return ()
         tq = ops.LATENT_MMA_ROWS // min(self.n_heads, ops.LATENT_MMA_ROWS)
         span = max_context if not self.window else min(max_context, self.window + tq)
-        return (ops.latent_attention_splits(n_rows, self.n_heads, self.kv_rank, span),)
+        return (ops.latent_attention_splits(n_rows, self.n_heads, self.kv_rank, span, self.row),)
 
     def forward(self, ctx, h, call):
         kv = ctx.kv_group(call.kv_group)

@@ -107,8 +107,8 @@ def decided_ids(path: Path, length: int, seed: int, chunk: int = 6) -> list:
             with torch.inference_mode():
                 pivinex_plain.forward(ids + piece, w, raw, margins=margins)
             T = len(ids) + n
-            per_run = np.asarray(margins).reshape(-1, T)[:, -n:]       # one row per run of a routed layer
-            if per_run.min() > ROUTER_MARGIN:
+            per_run = np.asarray(margins).reshape(-1, T)[:, -n:]       # one row per run of a routed layer that leaves outputs out
+            if per_run.size == 0 or per_run.min() > ROUTER_MARGIN:
                 break
         else:
             raise AssertionError("no piece of tokens gave decided router choices")
